@@ -46,8 +46,15 @@ class Model:
         eng = self.engine
         item = 4 if eng.dtype.itemsize == 4 else 2
         per_position = 0
+        def flat(entry):
+            if isinstance(entry, tuple):
+                for sub in entry:
+                    yield from flat(sub)
+            else:
+                yield entry
+
         for entry in eng.model.cache_requests():
-            for req in (entry if isinstance(entry, tuple) else (entry,)):
+            for req in flat(entry):
                 if req is not None and hasattr(req, "n_kv_heads"):
                     values = 0 if getattr(req, "values_in_keys", False) else (req.v_head_dim or req.head_dim)
                     per_position += req.n_kv_heads * (req.head_dim + values) * item

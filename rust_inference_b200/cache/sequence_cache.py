@@ -16,7 +16,9 @@ form a *group* with storage of its own:
                when the slot is handed out (a recurrent mixer's matrix state, for one).
 
 A mixer made of several mixers asks for several things at once: a tuple of requests, answered
-by a `CompositeLayer` whose `parts` are the answers in the same order, each in its own group.
+by a `CompositeLayer` whose `parts` are the answers in the same order, each in its own group.  A member
+may itself ask for several things (a recurrent mixer that keeps a matrix state and the last inputs of a
+short convolution): tuples nest, and so do the answers.
 
 All kv groups share one paging (`SlotPager`): position p of a slot lies in page
 `page_table[slot, p // page_size]` at offset `p % page_size`, in every layer.  The
@@ -99,20 +101,36 @@ class SequenceCache:
         # group layers by their needs
         self.groups: dict = {}
         self._layers: list = [None] * len(requests)
-        members: dict = {}                      # request -> [(cache layer, member of a composite or None)]
-        for i, req in enumerate(requests):
+        members: dict = {}                      # request -> [path]: the cache layer, then the places inside composites
+
+        def enlist(req, path):
+            """A composite's members are answered each in the group of its kind; a member may be a composite itself."""
             if isinstance(req, tuple):
                 for m, sub in enumerate(req):
-                    members.setdefault(sub, []).append((i, m))
-                self._layers[i] = CompositeLayer([None] * len(req), req)
+                    enlist(sub, path + (m,))
             elif req is not None:
-                members.setdefault(req, []).append((i, None))
+                members.setdefault(req, []).append(path)
 
-        def place(i, m, layer):
-            if m is None:
-                self._layers[i] = layer
-            else:
-                self._layers[i].parts[m] = layer
+        def composites(req, path):
+            layer = CompositeLayer([None] * len(req), req)
+            for m, sub in enumerate(req):
+                if isinstance(sub, tuple):
+                    layer.parts[m] = composites(sub, path + (m,))
+            return layer
+
+        for i, req in enumerate(requests):
+            enlist(req, (i,))
+            if isinstance(req, tuple):
+                self._layers[i] = composites(req, (i,))
+
+        def place(path, layer):
+            if len(path) == 1:
+                self._layers[path[0]] = layer
+                return
+            at = self._layers[path[0]]
+            for m in path[1:-1]:
+                at = at.parts[m]
+            at.parts[path[-1]] = layer
 
         for req, users in members.items():
             if isinstance(req, KVRequest):
@@ -126,19 +144,24 @@ class SequenceCache:
                 else:
                     v = torch.zeros(shape[:-1] + (req.v_head_dim or req.head_dim,), dtype=dtype, device=self.device)
                     self.groups[req] = (k, v)
-                for j, (i, m) in enumerate(users):
-                    place(i, m, KVLayer(k[j], v[j], req))
+                for j, path in enumerate(users):
+                    place(path, KVLayer(k[j], v[j], req))
             elif isinstance(req, StateRequest):
                 s = torch.zeros((len(users), n_slots) + tuple(req.shape), dtype=req.dtype,
                                 device=self.device)
                 self.groups[req] = (s,)
-                for j, (i, m) in enumerate(users):
-                    place(i, m, StateLayer(s[j], req))
+                for j, path in enumerate(users):
+                    place(path, StateLayer(s[j], req))
             else:
-                raise TypeError(f"cache layers {[i for i, _ in users]}: unknown request {req!r}")
-        for layer in self._layers:
+                raise TypeError(f"cache layers {[path[0] for path in users]}: unknown request {req!r}")
+
+        def freeze(layer):
             if isinstance(layer, CompositeLayer):
-                layer.parts = tuple(layer.parts)
+                layer.parts = tuple(freeze(part) for part in layer.parts)
+            return layer
+
+        for layer in self._layers:
+            freeze(layer)
 
     # ---- what the model reads --------------------------------------------
     def layer(self, index: int):

@@ -80,4 +80,4 @@ def load_spec(model_dir: str):
 
 def _ensure_builtin() -> None:
     # The built-in models register themselves on import.
-    from ..models import dense_decoder, lulisun, vadodra  # noqa: F401
+    from ..models import dense_decoder, lulisun, vadodra, redodra  # noqa: F401

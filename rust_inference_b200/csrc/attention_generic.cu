@@ -18,6 +18,14 @@
 // size when the values are the leading channels of the keys, vcache == kcache).  The result of token t
 // and head h goes to out + t * out_ld + h * out_hs (out_hs = v_hd: heads side by side in a token's row;
 // out_hs = n_tokens * v_hd with out_ld = v_hd: head-major, a head's tokens consecutive).
+//
+// Further forms of the score and of the mask, each off when its argument is zero or null:
+//   softcap     s <- softcap * tanh(s / softcap), after the scale
+//   dist        s <- s - r1_h * ln(1 + r2_h * (pos - j)): a bias that grows with the distance, two numbers per head
+//               (dist[h] = r1, dist[n_heads + h] = r2), taken off after the cap
+//   keep_first  with a window: the first keep_first positions of the sequence stay visible beyond it
+//   sink        the softmax's denominator also holds exp(sink_h): a learned number per head without key or value
+//   gate        the head's result is multiplied by sigmoid(gate[t * gate_ld + h])
 #include "common.cuh"
 
 using namespace ri;
@@ -34,7 +42,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
                     const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                     const int* __restrict__ seq_slot, T* __restrict__ out, int out_ld, int n_heads,
                     int n_kv_heads, int hd, int v_hd, int page_size, float scale, int window, int chunk,
-                    float out_scale, int v_ld, long long out_hs) {
+                    float out_scale, int v_ld, long long out_hs, float softcap, int keep_first,
+                    const float* __restrict__ sink, const float* __restrict__ dist, const T* gate, int gate_ld) {
     extern __shared__ float smem[];
     float* qs = smem;                 // [hd]
     float* ps = smem + hd;            // [THREADS]
@@ -51,18 +60,22 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
 
     int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     if (chunk > 0) first = max(first, pos - pos % chunk);
-    const int n_keys = pos + 1;
+    // the keys in the order they are visited: the kept first positions the window has left behind, then the window
+    const int n_kept = (window > 0 && keep_first > 0) ? min(keep_first, first) : 0;
+    const int n_keys = n_kept + pos + 1 - first;
+    const float r1 = dist != nullptr ? dist[h] : 0.f, r2 = dist != nullptr ? dist[n_heads + h] : 0.f;
 
     float m = -INFINITY, l = 0.f;
     float acc[MAX_ACC];
 #pragma unroll
     for (int a = 0; a < MAX_ACC; ++a) acc[a] = 0.f;
 
-    for (int c0 = first; c0 < n_keys; c0 += THREADS) {
-        const int j = c0 + tid;
+    for (int c0 = 0; c0 < n_keys; c0 += THREADS) {
+        const int jv = c0 + tid;
+        const int j = jv < n_kept ? jv : first + (jv - n_kept);
         float s = -INFINITY;
         __syncthreads();              // qs ready (first pass); ps / key_off free (later passes)
-        if (j < n_keys) {
+        if (jv < n_keys) {
             int page = pages[j / page_size];
             if (!RI_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;      // checked build: recorded, read from a page that exists
             const size_t row = ((size_t)page * n_kv_heads + kvh) * page_size + (j % page_size);
@@ -71,10 +84,12 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
             float dot = 0.f;
             for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            if (dist != nullptr) s -= r1 * log1pf(r2 * (float)(pos - j));
         }
         const float cmax = block_max(s, scratch);
         const float m_new = fmaxf(m, cmax);
-        const float p = (j < n_keys) ? expf(s - m_new) : 0.f;
+        const float p = (jv < n_keys) ? expf(s - m_new) : 0.f;
         ps[tid] = p;
         const float csum = block_sum(p, scratch);      // also makes ps / key_off visible
         const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -92,7 +107,19 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
             }
         }
     }
-    const float inv = out_scale / l;
+    if (sink != nullptr) {            // one more term of the denominator, with no value behind it
+        const float sk = sink[h];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int a = 0; a < MAX_ACC; ++a) acc[a] *= alpha;
+    }
+    float inv = out_scale / l;
+    if (gate != nullptr) {
+        const float gv = to_f32<T>(gate[(size_t)t * gate_ld + h]);
+        inv *= gv >= 0.f ? 1.f / (1.f + expf(-gv)) : expf(gv) / (1.f + expf(gv));
+    }
 #pragma unroll
     for (int a = 0; a < MAX_ACC; ++a) {
         const int d = tid + a * THREADS;
@@ -107,7 +134,8 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
                                 const int* token_seq, const int* seq_slot, void* out, int out_ld, int dtype,
                                 int n_tokens, int n_heads, int n_kv_heads, int hd, int v_hd, int page_size,
                                 long long cache_rows, float scale, int window, int chunk, float out_scale,
-                                int v_ld, long long out_hs, cudaStream_t stream) {
+                                int v_ld, long long out_hs, float softcap, int keep_first, const float* sink,
+                                const float* dist, const void* gate, int gate_ld, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads)
         return fail("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -117,6 +145,8 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
     if (v_ld < v_hd) return fail("attention: value rows %d apart hold %d values", v_ld, v_hd);
     if (v_hd > THREADS * MAX_ACC) return fail("attention: value head size %d exceeds %d", v_hd, THREADS * MAX_ACC);
     if (hd <= 0 || window < 0 || chunk < 0) return fail("attention: head size %d, window %d, chunk %d", hd, window, chunk);
+    if (keep_first < 0 || softcap < 0.f) return fail("attention: %d kept positions, a cap of %g", keep_first, softcap);
+    if (keep_first > 0 && chunk > 0) return fail("attention: kept first positions go with a window, not with chunks");
     if (cache_rows > 0x7fffffffLL) return fail("attention: cache of %lld rows exceeds 2^31", cache_rows);
     if (n_heads > 65535) return fail("attention: %d heads exceed the grid limit", n_heads);
     const size_t smem = (size_t)(hd + 2 * THREADS) * sizeof(float);
@@ -124,12 +154,14 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
     if (dtype == RI_F32)
         attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_ld, (const float*)kcache, (const float*)vcache, page_table, max_pages, token_pos,
-            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs);
+            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs,
+            softcap, keep_first, sink, dist, (const float*)gate, gate_ld);
     else if (dtype == RI_BF16)
         attn_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, page_table,
             max_pages, token_pos, token_seq, seq_slot, (__nv_bfloat16*)out, out_ld, n_heads, n_kv_heads, hd,
-            v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs);
+            v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs, softcap, keep_first, sink, dist,
+            (const __nv_bfloat16*)gate, gate_ld);
     else
         return fail("attention: unknown dtype %d", dtype);
     return check_launch("attention_generic");

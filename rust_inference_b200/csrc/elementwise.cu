@@ -621,7 +621,7 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
                                int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
                                int style, int write_kv, int rot, int v_hd, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot <= 0) rot = hd;
+    if (rot < 0) rot = hd;                // 0: nothing is rotated, keys and values are only stored
     if (v_hd <= 0) v_hd = hd;
     if (rot % 2 || rot > hd) return fail("rope_cache_write: %d rotated channels of a head of %d", rot, hd);
     if (style != 0 && style != 1) return fail("rope_cache_write: unknown style %d", style);

@@ -82,16 +82,20 @@ def decode_kernel(name: str):
 
 
 def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0, chunk=0,
-              v_head_dim=None, out_scale=1.0):
+              v_head_dim=None, out_scale=1.0, softcap=0.0, keep_first=0, sink=None, dist=None, gate=None):
     """out[t] = softmax(q_t K^T * scale) V over the keys 0..pos(t) of t's slot.  q is the
     leading n_heads*head_dim columns of `qkv`, already rotated.  `window`: only the last so many
     keys; `chunk`: only the keys of the query's own block of that many positions (counted from the
     start of the sequence); `v_head_dim`: values of another head size than keys; `out_scale`: a
     factor on the result.  The tensor-core kernels take a window or a chunk (as one signed span) and
-    equal head sizes; values of their own size, or both limits at once, are the generic kernel's."""
+    equal head sizes; values of their own size, or both limits at once, are the generic kernel's.
+    `softcap`, `keep_first`, `sink`, `dist`, `gate`: a cap on the scores, first positions that stay visible beyond
+    the window, a term without key in the softmax's denominator, a bias by distance and a gate per head on the
+    result (see `ops.attention_generic`)."""
     q_ld = qkv.shape[1]
     same_sizes = v_head_dim is None or v_head_dim == head_dim
-    if qkv.dtype == torch.bfloat16 and same_sizes and not (window and chunk):
+    plain = not (softcap or keep_first or sink is not None or dist is not None or gate is not None)
+    if qkv.dtype == torch.bfloat16 and same_sizes and not (window and chunk) and plain:
         span = window if window else -int(chunk or 0)
         decode = ctx.all_single
         if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
@@ -128,7 +132,8 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
         qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,
         head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, chunk=chunk or 0,
-        v_head_dim=v_head_dim, out_scale=out_scale)
+        v_head_dim=v_head_dim, out_scale=out_scale, softcap=softcap, keep_first=keep_first, sink=sink, dist=dist,
+        gate=gate)
 
 
 # RI_B200_LATENT_ATTENTION=generic keeps the generic kernel for attention over a shared latent (for comparisons)

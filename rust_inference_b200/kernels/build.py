@@ -35,6 +35,8 @@ MODULES = {
     "moe_tcgen05": "moe_tcgen05.cu",
     "latent": "latent.cu",
     "latent_attention_mma": "latent_attention_mma.cu",
+    "stream": "stream.cu",
+    "state_scan": "state_scan.cu",
     "wait_probe": "wait_probe.cu",
     "host_runtime": "host_runtime.cpp",
 }

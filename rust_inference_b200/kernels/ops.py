@@ -264,16 +264,18 @@ def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, to
     """Rotate q (in place) and k by the table rows of each token's position; store rotated k and v
     at the token's cache position.  kcache: one layer, [pages, kv heads, page_size, head_dim]; vcache
     the same with v_head_dim (default: head_dim).  rot_dims: only the first so many channels of a
-    head are rotated (default: all), the tables then having rot_dims/2 columns."""
+    head are rotated (default: all), the tables then having rot_dims/2 columns; 0: nothing is rotated (no
+    tables), keys and values are only stored.  A row of qkv may hold more columns after these (they are left
+    alone), and without write_kv only the query columns need to be there."""
     _need_cuda(qkv, cos, sin, token_pos, token_seq, seq_slot, page_table, kcache, vcache)
     n = qkv.shape[0]
     rot = head_dim if rot_dims is None else int(rot_dims)
     v_hd = head_dim if v_head_dim is None else int(v_head_dim)
-    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_hd,
-          "rope_cache_write: qkv must be [T, (heads + kv heads) * head_dim + kv heads * value head size]")
-    _need(0 < rot <= head_dim and rot % 2 == 0, "rope_cache_write: rotated channels must be even and at most head_dim")
-    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
-          and cos.is_contiguous() and sin.is_contiguous(),
+    _need(qkv.is_contiguous() and qkv.shape[1] >= n_heads * head_dim + ((n_kv_heads * (head_dim + v_hd)) if write_kv else 0),
+          "rope_cache_write: qkv must be [T, (heads + kv heads) * head_dim + kv heads * value head size (or more)]")
+    _need(0 <= rot <= head_dim and rot % 2 == 0, "rope_cache_write: rotated channels must be even and at most head_dim")
+    _need(rot == 0 or (cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
+                       and cos.is_contiguous() and sin.is_contiguous()),
           "rope_cache_write: tables must be float32 [positions, rotated channels / 2]")
     if write_kv:
         _need(kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous()
@@ -352,13 +354,25 @@ def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, to
                       seq_slot, out: torch.Tensor, *, n_tokens: int, n_heads: int, n_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: int = 0, chunk: int = 0,
                       v_head_dim: int | None = None, out_scale: float = 1.0, values_in_keys: bool = False,
-                      head_major: bool = False) -> torch.Tensor:
+                      head_major: bool = False, softcap: float = 0.0, keep_first: int = 0, sink=None, dist=None,
+                      gate=None) -> torch.Tensor:
     """Attention of every given token over its slot's cached keys 0..position (any sizes), limited to
     the last `window` keys and / or to the query's own block of `chunk` positions when those are not 0;
     values of head size v_head_dim (default: head_dim); the result times out_scale.  values_in_keys: the
     values are the first v_head_dim channels of the keys (vcache is not read).  head_major: out is
-    [heads, tokens, v_head_dim] instead of [tokens, heads * v_head_dim]."""
-    _need_cuda(q, kcache, vcache, page_table, token_pos, token_seq, seq_slot, out)
+    [heads, tokens, v_head_dim] instead of [tokens, heads * v_head_dim].  softcap: scores become
+    softcap * tanh(score / softcap); dist (float32 [2, heads]: r1, r2): r1 ln(1 + r2 (pos - key)) is taken off the
+    score; keep_first: with a window, the first so many positions stay visible; sink (float32 [heads]): one more
+    term exp(sink) in the softmax's denominator; gate ([tokens, >= heads] in q's dtype, a view is fine): the head's
+    result times the sigmoid of its entry."""
+    _need_cuda(q, kcache, vcache, page_table, token_pos, token_seq, seq_slot, out, sink, dist, gate)
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads),
+          "attention: sink must be float32 [heads]")
+    _need(dist is None or (dist.dtype == torch.float32 and dist.is_contiguous() and dist.numel() == 2 * n_heads),
+          "attention: dist must be float32 [2, heads]")
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[0] == n_tokens
+                           and gate.shape[1] >= n_heads), "attention: gate must be [tokens, heads] in q's dtype")
+    _need(not keep_first or window > 0, "attention: kept first positions go with a window")
     v_hd = head_dim if v_head_dim is None else int(v_head_dim)
     if values_in_keys:
         _need(v_hd <= head_dim, "attention: values inside keys cannot be wider than the keys")
@@ -376,7 +390,8 @@ def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, to
           c_int(out_ld), c_int(dtype_code(q.dtype)), c_int(n_tokens), c_int(n_heads),
           c_int(n_kv_heads), c_int(head_dim), c_int(v_hd), c_int(page_size), c_longlong(rows), c_float(scale),
           c_int(window), c_int(chunk), c_float(out_scale), c_int(head_dim if values_in_keys else v_hd),
-          c_longlong(out_hs), _stream())
+          c_longlong(out_hs), c_float(softcap), c_int(keep_first), _p(sink), _p(dist), _p(gate),
+          c_int(gate.stride(0) if gate is not None else 0), _stream())
     return out
 
 
@@ -776,4 +791,167 @@ def latent_attention_mma(q_wide: torch.Tensor, cache: torch.Tensor, page_table, 
     if n_splits > 1:
         global _launches
         _launches += 1                       # the merge is a kernel of its own
+    return out
+
+
+# ----------------------------------------------------------------------------
+# The hidden stream: norms without statistics, sums over depth, sums of normalised branches
+# ----------------------------------------------------------------------------
+def _f32_vec(t, n, what):
+    _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n, f"{what} must be float32 [{n}]")
+
+
+def dyt_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+             rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, :] = tanh(alpha * x[rows[r] or r, :]) * weight + bias.  x, weight, bias, alpha (one number) float32;
+    out float32 or bfloat16."""
+    _need_cuda(x, weight, bias, alpha, out, rows)
+    n_rows, n = out.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[-1] == n and out.is_contiguous(), "dyt_norm: bad shapes")
+    _f32_vec(weight, n, "dyt_norm: weight"); _f32_vec(bias, n, "dyt_norm: bias"); _f32_vec(alpha, 1, "dyt_norm: alpha")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() == n_rows, "dyt_norm: rows must be int32 [R]")
+    else:
+        _need(x.shape[0] >= n_rows, "dyt_norm: x has fewer rows than out")
+    _call("stream", "ri_dyt_norm", _p(x), _p(weight), _p(bias), _p(alpha), _p(rows), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(n), _stream())
+    return out
+
+
+def stream_update(stream_x: torch.Tensor, *, branch=None, branch_bias=None, post=None, history=None, depth_w=None,
+                  depth_index: int = 0, store_result: bool = True, next_norm=None, next_out=None) -> None:
+    """One pass over the float32 stream [T, n]: stream += post(branch + branch_bias) (post = (weight, bias, alpha) of a
+    tanh norm, None: the branch as it is; the branch buffer is left zeroed); with `history` (float32 [>= depth_index + 2,
+    T, n]) the result is stored as entry depth_index + 1 (if store_result) and the stream becomes
+    sum_j depth_w[j] * history[j] over j <= depth_index + 1; with next_norm = (weight, bias, alpha) next_out receives
+    that norm of the new stream."""
+    _need_cuda(stream_x, branch, branch_bias, history, depth_w, next_out)
+    t, n = stream_x.shape
+    _need(stream_x.dtype == torch.float32 and stream_x.is_contiguous(), "stream_update: the stream must be float32")
+    if branch is not None:
+        _need(branch.dtype == torch.float32 and branch.is_contiguous() and tuple(branch.shape) == (t, n), "stream_update: branch")
+    if branch_bias is not None:
+        _f32_vec(branch_bias, n, "stream_update: branch bias")
+    pw = pb = pa = nw = nb = na = None
+    if post is not None:
+        pw, pb, pa = post
+        _f32_vec(pw, n, "stream_update: norm weight"); _f32_vec(pb, n, "stream_update: norm bias"); _f32_vec(pa, 1, "stream_update: alpha")
+    if history is not None:
+        _need(history.dtype == torch.float32 and history.is_contiguous() and history.shape[0] >= depth_index + 2
+              and tuple(history.shape[1:]) == (t, n), "stream_update: history must be float32 [entries, T, n]")
+        _f32_vec(depth_w, depth_index + 2, "stream_update: depth weights")
+    next_dtype = 0
+    if next_norm is not None:
+        nw, nb, na = next_norm
+        _f32_vec(nw, n, "stream_update: next weight"); _f32_vec(nb, n, "stream_update: next bias"); _f32_vec(na, 1, "stream_update: next alpha")
+        _need(next_out is not None and next_out.is_contiguous() and tuple(next_out.shape) == (t, n), "stream_update: next_out")
+        next_dtype = dtype_code(next_out.dtype)
+    _call("stream", "ri_stream_update", _p(stream_x), _p(branch), _p(branch_bias), _p(pw), _p(pb), _p(pa), _p(history),
+          _p(depth_w), c_int(depth_index), c_int(1 if store_result else 0), _p(nw), _p(nb), _p(na),
+          _p(next_out if next_norm is not None else None), c_int(next_dtype), c_int(t), c_int(n), _stream())
+
+
+def normed_sum(members: list, out: torch.Tensor, eps: float, accumulate: bool = False) -> torch.Tensor:
+    """out (+)= sum over members (x, bias or None, weight, scale) of scale * rmsnorm(x + bias) * weight, row by row; every x
+    (float32 [T, n]) is left zeroed."""
+    t, n = out.shape
+    _need(1 <= len(members) <= 4, "normed_sum: one to four members")
+    _need(out.dtype == torch.float32 and out.is_contiguous(), "normed_sum: out must be float32")
+    xs, bs, ws, sc = (c_void_p * 4)(), (c_void_p * 4)(), (c_void_p * 4)(), (c_float * 4)()
+    for m, (x, bias, w, scale) in enumerate(members):
+        _need_cuda(x, bias, w)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (t, n), "normed_sum: member shape")
+        _f32_vec(w, n, "normed_sum: weight")
+        if bias is not None:
+            _f32_vec(bias, n, "normed_sum: bias")
+        xs[m], bs[m], ws[m], sc[m] = x.data_ptr(), (bias.data_ptr() if bias is not None else None), w.data_ptr(), float(scale)
+    _call("stream", "ri_normed_sum", xs, bs, ws, sc, c_int(len(members)), _p(out), c_int(t), c_int(n), c_float(eps),
+          c_int(1 if accumulate else 0), _stream())
+    return out
+
+
+def xielu(x: torch.Tensor, out: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """out = a_p x^2 + x/2 for x > 0, a_n (e^x - 1 - x) + x/2 otherwise, with a_p = softplus(pq[0]) and
+    a_n = 1/2 + softplus(pq[1]); float32 arithmetic; out may be x."""
+    _need_cuda(x, out, pq)
+    _need(x.dtype == out.dtype and x.is_contiguous() and out.is_contiguous() and x.numel() == out.numel(), "xielu: shapes")
+    _f32_vec(pq, 2, "xielu: parameters")
+    _call("stream", "ri_xielu", _p(x), _p(out), c_int(dtype_code(x.dtype)), _p(pq), c_longlong(x.numel()), _stream())
+    return out
+
+
+def add_row_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[t, :] += bias (float32)."""
+    _need_cuda(x, bias)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "add_row_bias: x must be float32 [T, n]")
+    _f32_vec(bias, x.shape[1], "add_row_bias: bias")
+    _call("stream", "ri_add_row_bias", _p(x), _p(bias), c_int(x.shape[0]), c_int(x.shape[1]), _stream())
+    return x
+
+
+# ----------------------------------------------------------------------------
+# Recurrent mixers with one decay per head (state space, gated delta rule)
+# ----------------------------------------------------------------------------
+def scan_prepare(z: torch.Tensor, *, conv_col: int, conv_ch: int, taps: torch.Tensor, conv_bias, conv_state: torch.Tensor,
+                 unit_heads: int, unit_dim: int, scaled_heads: int, unit_scale: float, heads: int, decay_col: int,
+                 step_col: int, a_log: torch.Tensor, dt_bias: torch.Tensor, out: torch.Tensor, cu_seqlens, token_seq,
+                 seq_slot, n_seqs: int) -> torch.Tensor:
+    """Per token of z (float32 [T, ld]): the short causal convolution (taps float32 [conv_ch, K], last column the
+    current token's; bias or None) and silu of the columns conv_col .. conv_col + conv_ch, reading the inputs before
+    the step from conv_state (float32 [slots, K - 1, conv_ch]) and moving those on; the first unit_heads heads of
+    unit_dim channels made unit vectors (the first scaled_heads of them times unit_scale); per head the decay
+    exp(-exp(a_log) * softplus(z[decay_col + h] + dt_bias)) and the step (sigmoid(z[step_col + h]), or with
+    step_col < 0 the softplus itself).  out: float32 [T, >= conv_ch + 2 heads] = [channels | decays | steps]."""
+    _need_cuda(z, taps, conv_bias, conv_state, a_log, dt_bias, out, cu_seqlens, token_seq, seq_slot)
+    t = z.shape[0]
+    k = taps.shape[1]
+    _need(z.dtype == torch.float32 and z.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+          and out.shape[0] == t, "scan_prepare: z and out must be float32 [T, .]")
+    _need(taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[0] == conv_ch, "scan_prepare: taps")
+    _need(conv_bias is None or (conv_bias.dtype == torch.float32 and conv_bias.numel() == conv_ch), "scan_prepare: bias")
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+          and tuple(conv_state.shape[1:]) == (max(k - 1, 0), conv_ch), "scan_prepare: carried inputs must be [slots, K - 1, channels]")
+    _f32_vec(a_log, heads, "scan_prepare: A_log"); _f32_vec(dt_bias, heads, "scan_prepare: dt_bias")
+    _call("state_scan", "ri_scan_prepare", _p(z), c_int(z.shape[1]), c_int(conv_col), c_int(conv_ch), _p(taps), _p(conv_bias),
+          c_int(k), _p(conv_state), c_int(unit_heads), c_int(unit_dim), c_int(scaled_heads), c_float(unit_scale), c_int(heads),
+          c_int(decay_col), c_int(step_col), _p(a_log), _p(dt_bias), _p(out), c_int(out.shape[1]), _p(cu_seqlens),
+          _p(token_seq), _p(seq_slot), c_int(t), c_int(n_seqs), _stream())
+    return out
+
+
+def state_scan(u: torch.Tensor, state: torch.Tensor, o: torch.Tensor, cu_seqlens, seq_slot, *, n_seqs: int, heads: int,
+               groups: int, dim: int, vdim: int, q_col: int, k_col: int, v_col: int, decay_col: int, step_col: int,
+               delta: bool, skip=None, longest_run: int = 0) -> torch.Tensor:
+    """The recurrence over every sequence's new tokens from its slot's state (float32 [slots, heads, dim, vdim]), which
+    moves on.  u: float32 [T, ld] with the columns of queries and keys ([groups, dim] each), values ([heads, vdim]),
+    decays and steps ([heads] each); o: float32 [T, heads * vdim].  delta: the gated delta rule
+    (S <- a S; S += k (step (v - S^T k))^T); else S <- a S + k (step v)^T and o += skip * v."""
+    _need_cuda(u, state, o, cu_seqlens, seq_slot, skip)
+    _need(u.dtype == torch.float32 and u.is_contiguous() and o.dtype == torch.float32 and o.is_contiguous()
+          and tuple(o.shape) == (u.shape[0], heads * vdim), "state_scan: u and o must be float32")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "state_scan: state must be float32 [slots, heads, dim, vdim]")
+    if skip is not None:
+        _f32_vec(skip, heads, "state_scan: skip")
+    _call("state_scan", "ri_state_scan", _p(u), c_int(u.shape[1]), c_int(q_col), c_int(k_col), c_int(v_col), c_int(decay_col),
+          c_int(step_col), _p(skip), _p(state), _p(o), _p(cu_seqlens), _p(seq_slot), c_int(n_seqs), c_int(heads), c_int(groups),
+          c_int(dim), c_int(vdim), c_int(1 if delta else 0), c_int(longest_run), _stream())
+    return o
+
+
+def gated_group_norm(x: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, out: torch.Tensor, *,
+                     groups: int, group_size: int, gate_first: bool, eps: float, out_scale: float = 1.0) -> torch.Tensor:
+    """Per token and group of group_size channels of x (float32 [T, groups * group_size]): RMS norm over the group times
+    weight[channel % len(weight)], and a gate silu(gate[t, gate_col + channel]) applied before the norm (gate_first) or
+    after it; the result times out_scale into out (float32 or bfloat16)."""
+    _need_cuda(x, gate, weight, out)
+    t = x.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == groups * group_size, "gated_group_norm: x")
+    _need(gate.dtype == torch.float32 and gate.is_contiguous() and gate.shape[0] == t
+          and gate.shape[1] >= gate_col + groups * group_size, "gated_group_norm: gate")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous(), "gated_group_norm: weight")
+    _need(out.is_contiguous() and tuple(out.shape) == (t, groups * group_size), "gated_group_norm: out")
+    _call("state_scan", "ri_gated_group_norm", _p(x), c_int(x.shape[1]), _p(gate), c_int(gate.shape[1]), c_int(gate_col), _p(weight),
+          c_int(weight.numel()), _p(out), c_int(dtype_code(out.dtype)), c_int(t), c_int(groups), c_int(group_size),
+          c_int(1 if gate_first else 0), c_float(eps), c_float(out_scale), _stream())
     return out

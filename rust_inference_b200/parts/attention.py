@@ -28,14 +28,25 @@ class GQAttention(Mixer):
     # `qk_norm_eps`: every q and k head is RMS-normalised before the rotation, with one weight of head_dim
     # values for the q heads and one for the k heads (`names`: q_norm, k_norm).  `values_from_keys`: there is
     # no value projection; a position's values are its keys as projected, before norm and rotation.
+    # Forms of the score, the mask and the result (all off by default): `softcap` (scores become
+    # softcap * tanh(score / softcap) after the scale); `distance_bias` (r1_h ln(1 + r2_h * distance) is taken off the
+    # capped score, two learned numbers per head, `names`: r1, r2); `keep_first` (with a window: the first so many
+    # positions of the sequence stay visible beyond it, at their true positions); `sink` (the softmax's denominator
+    # also holds exp(sink_h), a learned number per head without key or value); `head_gate` (the head's result times
+    # sigmoid(W_g x)_h, one more row per head in the projection, `names`: gate); `o_bias` (a bias on the output
+    # projection, `names`: o_bias); `own_kv` False: the layer has no key and value projections and attends over the
+    # cache of the layer the schedule gives it, with its own queries.
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
               "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "o_bias": "o_proj.bias", "sink": "sinks",
+              "gate": "gate_proj.weight", "r1": "distance_r1", "r2": "distance_r2"}
 
     def __init__(self, *, n_heads: int, n_kv_heads: int, head_dim: int, qkv_bias: bool,
                  position: PartSpec, window: int | None = None, v_head_dim: int | None = None,
                  scale: float | None = None, chunk: int | None = None, out_scale: float = 1.0,
                  names: dict | None = None, qk_norm_eps: float | None = None, values_from_keys: bool = False,
+                 softcap: float = 0.0, distance_bias: bool = False, keep_first: int = 0, sink: bool = False,
+                 head_gate: bool = False, o_bias: bool = False, own_kv: bool = True,
                  hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if n_heads % n_kv_heads:
@@ -56,6 +67,19 @@ class GQAttention(Mixer):
         if self.values_from_keys and self.qkv_bias:
             raise ValueError("values taken from keys and projection biases are not combined")
         self.q_norm = self.k_norm = None
+        self.softcap, self.keep_first = float(softcap), int(keep_first or 0)
+        self.distance_bias, self.sink, self.head_gate = bool(distance_bias), bool(sink), bool(head_gate)
+        self.o_bias, self.own_kv = bool(o_bias), bool(own_kv)
+        if self.softcap < 0 or self.keep_first < 0:
+            raise ValueError(f"a score cap and a number of kept positions are not negative, found {softcap}, {keep_first}")
+        if self.keep_first and window is None:
+            raise ValueError("kept first positions go with a window")
+        if not self.own_kv and (self.values_from_keys or self.qk_norm_eps is not None):
+            raise ValueError("a layer without keys of its own has no key norm and no values taken from keys")
+        # what only the general path (one projection, then the position encoding, then attention with these forms) does
+        self.extended = bool(self.softcap or self.distance_bias or self.keep_first or self.sink or self.head_gate
+                             or not self.own_kv)
+        self.sinks = self.dist = self.b_o = None
         self.window = window
         self.chunk = chunk
         self.out_scale = float(out_scale)
@@ -75,38 +99,78 @@ class GQAttention(Mixer):
         }
         if self.values_from_keys:
             del specs[nm["v"]]
+        if not self.own_kv:
+            del specs[nm["k"]], specs[nm["v"]]
+        if self.head_gate:
+            specs[nm["gate"]] = TensorSpec((self.n_heads, h))
+        if self.sink:
+            specs[nm["sink"]] = TensorSpec((self.n_heads,), role="vector", init="zeros")
+        if self.distance_bias:
+            specs[nm["r1"]] = TensorSpec((self.n_heads,), role="vector", init="ones")
+            specs[nm["r2"]] = TensorSpec((self.n_heads,), role="vector", init="ones")
+        if self.o_bias:
+            specs[nm["o_bias"]] = TensorSpec((h,), role="vector")
         if self.qk_norm_eps is not None:
             specs[nm["q_norm"]] = TensorSpec((self.head_dim,), role="vector", init="ones")
             specs[nm["k_norm"]] = TensorSpec((self.head_dim,), role="vector", init="ones")
         if self.qkv_bias:
             specs[nm["q_bias"]] = TensorSpec((self.q_dim,), role="vector")
-            specs[nm["k_bias"]] = TensorSpec((self.kv_dim,), role="vector")
-            specs[nm["v_bias"]] = TensorSpec((self.v_dim,), role="vector")
+            if self.own_kv:
+                specs[nm["k_bias"]] = TensorSpec((self.kv_dim,), role="vector")
+                specs[nm["v_bias"]] = TensorSpec((self.v_dim,), role="vector")
         return specs
 
     def set_tensors(self, tensors):
         nm = self.names
         # one matrix for the three projections: one pass over x
-        mats = [tensors[nm["q"]], tensors[nm["k"]]] + ([] if self.values_from_keys else [tensors[nm["v"]]])
+        mats = [tensors[nm["q"]]]
+        if self.own_kv:
+            mats += [tensors[nm["k"]]] + ([] if self.values_from_keys else [tensors[nm["v"]]])
+        if self.head_gate:
+            mats.append(tensors[nm["gate"]])           # one more row per head: the gates come out of the same product
         self.w_qkv = linear.Weight(torch.cat(mats, dim=0))
+        if self.sink:
+            self.sinks = tensors[nm["sink"]].contiguous()
+        if self.distance_bias:
+            self.dist = torch.stack([tensors[nm["r1"]], tensors[nm["r2"]]], dim=0).contiguous()
+        if self.o_bias:
+            self.b_o = tensors[nm["o_bias"]].contiguous()
+            self.b_o_scaled = self.b_o if self.out_scale == 1.0 else self.b_o * self.out_scale
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = tensors[nm["q_norm"]].contiguous(), tensors[nm["k_norm"]].contiguous()
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors[nm["q_bias"]], tensors[nm["k_bias"]], tensors[nm["v_bias"]]],
-                                   dim=0).contiguous()
+            biases = [tensors[nm["q_bias"]]] + ([tensors[nm["k_bias"]], tensors[nm["v_bias"]]] if self.own_kv else [])
+            if self.head_gate:
+                biases.append(torch.zeros(self.n_heads, dtype=biases[0].dtype, device=biases[0].device))
+            self.b_qkv = torch.cat(biases, dim=0).contiguous()
         self.w_o = linear.Weight(tensors[nm["o"]])
 
     def get_tensors(self):
         q, kv, nm = self.q_dim, self.kv_dim, self.names
         w = self.w_qkv.t
-        out = {nm["q"]: w[:q], nm["k"]: w[q:q + kv], nm["v"]: w[q + kv:], nm["o"]: self.w_o.t}
-        if self.values_from_keys:
-            del out[nm["v"]]
+        out = {nm["q"]: w[:q], nm["o"]: self.w_o.t}
+        at = q
+        if self.own_kv:
+            out[nm["k"]] = w[q:q + kv]
+            at = q + kv
+            if not self.values_from_keys:
+                out[nm["v"]] = w[at:at + self.v_dim]
+                at += self.v_dim
+        if self.head_gate:
+            out[nm["gate"]] = w[at:at + self.n_heads]
+        if self.sink:
+            out[nm["sink"]] = self.sinks
+        if self.distance_bias:
+            out[nm["r1"]], out[nm["r2"]] = self.dist[0], self.dist[1]
+        if self.o_bias:
+            out[nm["o_bias"]] = self.b_o
         if self.qk_norm_eps is not None:
             out[nm["q_norm"]], out[nm["k_norm"]] = self.q_norm, self.k_norm
         if self.qkv_bias:
             b = self.b_qkv
-            out.update({nm["q_bias"]: b[:q], nm["k_bias"]: b[q:q + kv], nm["v_bias"]: b[q + kv:]})
+            out[nm["q_bias"]] = b[:q]
+            if self.own_kv:
+                out.update({nm["k_bias"]: b[q:q + kv], nm["v_bias"]: b[q + kv:q + kv + self.v_dim]})
         return out
 
     def prepare(self, max_positions):
@@ -118,9 +182,14 @@ class GQAttention(Mixer):
 
     def forward(self, x, residual, ctx, cache_layer, writes_cache):
         n = x.shape[0]
-        width = self.q_dim + self.kv_dim + (0 if self.values_from_keys else self.v_dim)
+        if not writes_cache and self.own_kv:
+            raise ValueError("a layer with key and value projections writes its own cache")
+        kv_width = (self.kv_dim + (0 if self.values_from_keys else self.v_dim)) if self.own_kv else 0
+        gate_col = self.q_dim + kv_width
+        width = gate_col + (self.n_heads if self.head_gate else 0)
         special = self.values_from_keys or self.qk_norm_eps is not None
-        usual = self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False) and not special
+        usual = (self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False) and not special
+                 and not self.extended)
         from_acc = getattr(self.position, "apply_and_store_from_accumulators", None) if usual else None
         if from_acc is not None and linear.wants_split(x, self.w_qkv):
             # a small step: the projection is split over K into float32 accumulators, and the
@@ -144,10 +213,15 @@ class GQAttention(Mixer):
             else:
                 self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
                                               n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
-                                              write_kv=writes_cache, **extra)
+                                              write_kv=writes_cache and self.own_kv, **extra)
         mixed = ctx.buffer("attn_out", (n, self.o_dim), self.dtype)
         attn_kernels.attention(qkv, cache_layer, mixed, ctx, n_heads=self.n_heads,
                                n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,
                                window=self.window or 0, chunk=self.chunk or 0, v_head_dim=self.v_head_dim,
-                               out_scale=self.out_scale)
+                               out_scale=self.out_scale, softcap=self.softcap, keep_first=self.keep_first,
+                               sink=self.sinks, dist=self.dist,
+                               gate=qkv[:, gate_col:gate_col + self.n_heads] if self.head_gate else None)
         linear.into_residual(mixed, self.w_o, residual, ctx)
+        if self.o_bias:
+            from ..kernels import ops
+            ops.add_row_bias(residual, self.b_o_scaled)

@@ -115,6 +115,22 @@ class Head(Part):
         return 0
 
 
+class DepthMix(Part):
+    """What a layer hands on to the next one, as a function of its own result and of the results of the layers before
+    it.  The arrangement calls `enter` before the layer touches the stream and `leave` when the stream holds the layer's
+    result; `leave` replaces the stream by what goes on.  A part that can join an elementwise pass over the stream says so
+    with `fused(ctx, stream)` (keyword arguments of `ops.stream_update`, or None)."""
+
+    def enter(self, stream: torch.Tensor, ctx) -> None:
+        pass
+
+    def leave(self, stream: torch.Tensor, ctx) -> None:
+        raise NotImplementedError
+
+    def fused(self, ctx, stream: torch.Tensor):
+        return None
+
+
 class Arrangement:
     """How a layer's parts are wired.  Built from the already-built parts, one per role.
 

@@ -1,10 +1,11 @@
-"""Gated feed-forwards without biases: SwiGLU (mlp.rs:31-46), down( silu(gate x) * (up x) ), and the bounded
-form down( g sigmoid(alpha g) (u + shift) ) with g = min(gate x, limit), u = clamp(up x, -limit, limit)."""
+"""Feed-forwards without biases: SwiGLU (mlp.rs:31-46), down( silu(gate x) * (up x) ), the bounded gated
+form down( g sigmoid(alpha g) (u + shift) ) with g = min(gate x, limit), u = clamp(up x, -limit, limit), and the
+ungated form down( act(up x) ) with a learned activation."""
 from __future__ import annotations
 
 import torch
 
-from ..kernels import linear
+from ..kernels import linear, ops
 from .base import FeedForward
 from .registry import register
 from .spec import TensorSpec
@@ -77,4 +78,42 @@ class BoundedGLU(FeedForward):
     def forward(self, x, residual, ctx):
         act = ctx.buffer("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
         linear.gated(x, self.w_gate, self.w_up, act, ctx, form=self.form)
+        linear.into_residual(act, self.w_down, residual, ctx)
+
+
+@register("feed_forward", "dense_act")
+class DenseActivation(FeedForward):
+    """out = W_down act(W_up x), no gate.  `activation` "xielu": with the two learned numbers p, q of the tensor `act`,
+    act(z) = softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 otherwise (float32
+    arithmetic on the projection's result; p and q are read on the device).  `names`: up, down, act below the prefix."""
+
+    _NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "act": "act"}
+    ACTIVATIONS = ("xielu",)
+
+    def __init__(self, *, intermediate_size: int, activation: str = "xielu", names: dict | None = None,
+                 hidden_size: int, dtype, device):
+        super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"dense_act: unknown activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.intermediate_size, self.activation = int(intermediate_size), activation
+        self.names = dict(self._NAMES, **(names or {}))
+        self.w_up = self.w_down = self.act = None
+
+    def tensor_specs(self):
+        i, h, nm = self.intermediate_size, self.hidden_size, self.names
+        return {nm["up"]: TensorSpec((i, h)), nm["down"]: TensorSpec((h, i)), nm["act"]: TensorSpec((2,), role="vector")}
+
+    def set_tensors(self, tensors):
+        nm = self.names
+        self.w_up, self.w_down = linear.Weight(tensors[nm["up"]]), linear.Weight(tensors[nm["down"]])
+        self.act = tensors[nm["act"]].contiguous()
+
+    def get_tensors(self):
+        nm = self.names
+        return {nm["up"]: self.w_up.t, nm["down"]: self.w_down.t, nm["act"]: self.act}
+
+    def forward(self, x, residual, ctx):
+        act = ctx.buffer("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
+        linear.project(x, self.w_up, act, ctx)
+        ops.xielu(act, act, self.act)
         linear.into_residual(act, self.w_down, residual, ctx)

@@ -1,4 +1,5 @@
-"""RMSNorm, with eps as a parameter (rmsnorm.rs:4-29, math.rs:237-256)."""
+"""Norms of the hidden stream: RMSNorm with eps as a parameter (rmsnorm.rs:4-29, math.rs:237-256), a layer norm, and a
+norm without statistics (a scaled tanh of every element)."""
 from __future__ import annotations
 
 import torch
@@ -72,3 +73,36 @@ class LayerNorm(Norm):
 
     def forward(self, x, out, rows=None):
         return ops.layernorm(x, self.weight, self.eps, out, rows)
+
+
+@register("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * weight + bias: no mean and no variance is computed, every element is squashed by itself
+    (alpha is one learned number).  float32 arithmetic.  `weight_name`, `bias_name` and `alpha_name` are the tensors'
+    names below the part's prefix.  Because no element needs its row, this norm joins the elementwise passes over the
+    stream (`fused()` gives the three tensors such a pass needs)."""
+
+    def __init__(self, *, weight_name: str = "weight", bias_name: str = "bias", alpha_name: str = "alpha",
+                 hidden_size: int, dtype, device):
+        super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+        self.weight_name, self.bias_name, self.alpha_name = weight_name, bias_name, alpha_name
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self):
+        return {self.weight_name: TensorSpec((self.hidden_size,), role="vector", init="ones"),
+                self.bias_name: TensorSpec((self.hidden_size,), role="vector", init="zeros"),
+                self.alpha_name: TensorSpec((), role="vector", init="ones")}
+
+    def set_tensors(self, tensors):
+        self.weight = tensors[self.weight_name].contiguous()
+        self.bias = tensors[self.bias_name].contiguous()
+        self.alpha = tensors[self.alpha_name].reshape(1).contiguous()
+
+    def get_tensors(self):
+        return {self.weight_name: self.weight, self.bias_name: self.bias, self.alpha_name: self.alpha.reshape(())}
+
+    def fused(self):
+        return self.weight, self.bias, self.alpha
+
+    def forward(self, x, out, rows=None):
+        return ops.dyt_norm(x, self.weight, self.bias, self.alpha, out, rows)

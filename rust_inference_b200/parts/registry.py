@@ -12,11 +12,13 @@ Interfaces (see `parts.base`):
   arrangement       Arrangement (how norms, mixer, feed-forward and residuals are wired; declares its roles)
   embedding         Embedding (token ids -> hidden stream)
   head              Head (hidden stream -> logits)
+  depth             DepthMix (what a layer hands on, as a function of the results of all layers so far)
 """
 from __future__ import annotations
 
 _REGISTRIES: dict[str, dict] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
+    "depth": {},
 }
 
 
@@ -54,3 +56,4 @@ def kinds(category: str) -> list[str]:
 def _ensure_builtin() -> None:
     from . import norm, rope, attention, feed_forward, block, embedding, head  # noqa: F401
     from . import recurrence, parallel_mixer, routed_experts, latent_attention  # noqa: F401
+    from . import depth, state_space, delta_rule  # noqa: F401

@@ -100,3 +100,18 @@ class RotaryEncoding(PositionEncoding):
                                  ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
                                  n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
                                  style=self.style, write_kv=write_kv)
+
+
+@register("position", "unrotated")
+class Unrotated(PositionEncoding):
+    """No rotation: queries stay as projected, keys and values go into the cache as they are.  For mixers whose positions
+    enter elsewhere (a bias on the scores that depends on the distance), or nowhere."""
+
+    partial = True          # the usual fused paths rotate whole heads
+
+    def apply_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv, v_head_dim=None):
+        if not write_kv:
+            return
+        ops.rope_cache_write(qkv, None, None, ctx.token_pos, ctx.token_seq, ctx.seq_slot, ctx.page_table, cache_layer.k,
+                             cache_layer.v, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+                             page_size=ctx.page_size, style=0, write_kv=True, rot_dims=0, v_head_dim=v_head_dim)

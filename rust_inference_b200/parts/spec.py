@@ -123,7 +123,7 @@ class TensorSpec:
 
     role  "matrix" (kept in the run dtype), "vector" (norm weights and biases: kept in
           float32 on the device whatever they were stored as) or "table" (integers, int32);
-    init  how the random-weights mode fills it: "normal", "ones" or "zeros".
+    init  how the random-weights mode fills it: "normal", "ones", "zeros" or "unit_last" (zeros, the last entry 1).
     """
     shape: tuple
     role: str = "matrix"

@@ -113,6 +113,9 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float 
                 t += torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, norm_std, generator=gen)
         elif spec.init == "zeros":
             t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "unit_last":
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+            t[..., -1] = 1.0
         elif spec.init == "normal":
             t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
         else:
@@ -134,6 +137,9 @@ def _random_tensors_on_device(expected, seed, std, matrix_dtype, device, norm_st
             t = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif spec.init == "zeros":
             t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "unit_last":
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+            t[..., -1] = 1.0
         elif spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
             if norm_std > 0.0:
