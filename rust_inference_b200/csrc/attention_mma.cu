@@ -799,6 +799,172 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// prefill / continuation / decode with further forms of the score, the mask and the result (the generic
+// kernel's, see attention_generic.cu), 64 query tokens of one head per CTA as above:
+//   softcap     s <- softcap * tanh(s / softcap) after the scale (accurate tanhf)
+//   dist        s <- s - r1_h * ln(1 + r2_h * (pos - key)), dist[h] = r1, dist[n_heads + h] = r2
+//   keep_first  with a window: the first keep_first positions stay visible beyond it.  The CTA walks the pages of
+//               the kept positions that lie before its window's first page, then the window's pages
+//   sink        one more term exp(sink_h) in the softmax's denominator, without key or value
+//   gate        the head's result times sigmoid(gate[t * gate_ld + h])
+// Scores, their cap and bias, the softmax's statistics and weights are float32.  A weight enters the product with
+// the values as the sum of two bfloat16 numbers (its rounding and the rounding of what that left over, 16
+// significant bits together), so the values' own bfloat16 rounding is the only one of that size in the sum.
+// window >= 0 only (no blocks of positions).
+// ---------------------------------------------------------------------------------------------
+struct ScoreForms {
+    float softcap;             // 0: none
+    int keep_first;
+    const float* sink;         // [n_heads] or null
+    const float* dist;         // [2][n_heads] or null
+    const __nv_bfloat16* gate; // [tokens, gate_ld] or null
+    int gate_ld;
+    float out_scale;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_forms_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
+                          const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
+                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                          const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale, int window,
+                          ScoreForms f, __nv_bfloat16* __restrict__ out, int out_ld) {
+    constexpr int TILE = PAGE * HD * 2;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t kv_base = smem_u32(smem);
+    const uint32_t q_tile = kv_base + 4 * TILE;           // [64][HD]
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const float r1 = f.dist != nullptr ? f.dist[h] : 0.f, r2 = f.dist != nullptr ? f.dist[n_heads + h] : 0.f;
+    const float sink = f.sink != nullptr ? f.sink[h] : -INFINITY;
+    const float inv_cap = f.softcap > 0.f ? 1.f / f.softcap : 0.f;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
+    const int q0 = blockIdx.x * 64;
+    if (q0 >= n_new) return;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int start = seq_start[b];
+    const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
+    const int rows = min(64, n_new - q0);
+    const int keep = window > 0 ? f.keep_first : 0;
+
+    const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
+    const int pg_begin = first_visible_key(pos_lo, window) / PAGE, pg_end = pos_hi / PAGE + 1;
+    const int kept_pages = min(pg_begin, (keep + PAGE - 1) / PAGE);    // pages of kept positions before the window's
+    const int n_pages = kept_pages + pg_end - pg_begin;
+    auto page_of = [&](int i) { return i < kept_pages ? i : pg_begin + i - kept_pages; };
+
+    for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += THREADS) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)(tok0 + q0 + r) * q_ld + (size_t)h * HD + c * 8);
+        *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
+    }
+    auto issue = [&](int i, int buf) {
+        int page = pages[page_of(i)];
+        if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;
+        const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * HD;
+        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
+        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
+        cp_async_commit();
+    };
+    issue(0, 0);
+    __syncthreads();
+
+    const bool idle = warp * 16 >= rows;                  // a decode step's CTA has one row: three warps only help to load
+    uint32_t qf[HD / 16][4];
+    {
+        const int row = warp * 16 + (lane & 15), half = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(q_tile + tile_off<HD>(row, ks * 2 + half), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+    const int r0 = warp * 16 + g, r1_row = r0 + 8;
+    const int p0 = start + q0 + r0, p1 = start + q0 + r1_row;
+    const int warp_pos_lo = start + q0 + warp * 16, warp_pos_hi = min(warp_pos_lo + 15, pos_hi);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+    for (int i = 0; i < n_pages; ++i) {
+        const int buf = i & 1;
+        if (i + 1 < n_pages) {
+            issue(i + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
+        const int key_lo = page_of(i) * PAGE, key_hi = key_lo + PAGE - 1;
+        const bool any = !idle && key_lo <= warp_pos_hi && (key_hi >= first_visible_key(warp_pos_lo, window) || key_lo < keep);
+        if (any) {
+            const bool full = key_hi <= warp_pos_lo && (key_lo >= first_visible_key(warp_pos_hi, window) || key_hi < keep);
+#pragma unroll
+            for (int kb = 0; kb < PAGE / 16; ++kb) {
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                qk_16keys<HD>(qf, ktile, kb * 16, s);
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key_lo + kb * 16 + t * 8 + 2 * tq + (e & 1);
+                        const int pos = (e & 2) ? p1 : p0;
+                        const bool vis = full || (key <= pos && (key >= first_visible_key(pos, window) || key < keep));
+                        float v = s[t][e] * scale;
+                        if (f.softcap > 0.f) v = f.softcap * tanhf(v * inv_cap);
+                        if (f.dist != nullptr) v -= r1 * log1pf(r2 * (float)max(pos - key, 0));
+                        s[t][e] = vis ? v : -INFINITY;
+                    }
+                softmax_update<2, HD / 8>(s, m, l, o);
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float a = s[c >> 1][2 * (c & 1)], bb = s[c >> 1][2 * (c & 1) + 1];
+                    const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(bb);
+                    hi[c] = pack_bf16(a, bb);
+                    lo[c] = pack_bf16(a - __bfloat162float(ah), bb - __bfloat162float(bh));
+                }
+                pv_16keys<HD>(hi, vtile, kb * 16, o);
+                pv_16keys<HD>(lo, vtile, kb * 16, o);
+            }
+        }
+        __syncthreads();
+    }
+    if (idle) return;
+    float inv[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float scale_o = 1.f;
+        if (f.sink != nullptr) {                           // one more term of the denominator, with no value behind it
+            const float m_new = fmaxf(m[half], sink);
+            scale_o = expf(m[half] - m_new);
+            l[half] = l[half] * scale_o + expf(sink - m_new);
+        }
+        inv[half] = f.out_scale * scale_o / l[half];
+        const int r = half ? r1_row : r0;
+        if (f.gate != nullptr && r < rows) {
+            const float gv = __bfloat162float(f.gate[(size_t)(tok0 + q0 + r) * f.gate_ld + h]);
+            inv[half] *= gv >= 0.f ? 1.f / (1.f + expf(-gv)) : expf(gv) / (1.f + expf(gv));
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) {
+        const int d = t * 8 + 2 * tq;
+        if (r0 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + q0 + r0) * out_ld + (size_t)h * HD + d) =
+                pack_bf16(o[t][0] * inv[0], o[t][1] * inv[0]);
+        if (r1_row < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + q0 + r1_row) * out_ld + (size_t)h * HD + d) =
+                pack_bf16(o[t][2] * inv[1], o[t][3] * inv[1]);
+    }
+}
+
 template <int HD>
 int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
                   const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
@@ -922,6 +1088,22 @@ int launch_prefill(const void* q, int q_ld, const void* kc, const void* vc, cons
     return check_launch(e, "attn_prefill");
 }
 
+template <int HD>
+int launch_prefill_forms(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
+                         const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new,
+                         int n_heads, int n_kv_heads, float scale, int window, ScoreForms f, void* out, int out_ld,
+                         cudaStream_t stream) {
+    constexpr int SMEM = 4 * PAGE * HD * 2 + 64 * HD * 2;
+    static PerDeviceOnce configured;
+    if (int rc = raise_dynamic_smem(attn_prefill_forms_kernel<HD>, SMEM, configured, "attention")) return rc;
+    dim3 grid((max_new + 63) / 64, n_heads, n_seqs);
+    cudaError_t e = launch_dependent(
+        attn_prefill_forms_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_start, cu_seqlens,
+        n_heads, n_kv_heads, scale, window, f, (__nv_bfloat16*)out, out_ld);
+    return check_launch(e, "attn_prefill_forms");
+}
+
 int check_common(int hd, int page_size, int n_heads, int n_kv_heads, int q_ld, int out_ld, const void* q,
                  const void* out) {
     if (hd != 64 && hd != 128) return fail("attention_mma: head_dim %d is not 64 or 128", hd);
@@ -1028,6 +1210,27 @@ RI_API int ri_attention_prefill(const void* q, int q_ld, const void* kcache, con
                                   max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
     return launch_prefill<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
                                max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
+}
+
+// The same for scores with a cap, a bias by distance, kept first positions, a sink and a gate per head (each off when
+// zero or null); window >= 0.  Whole prompts, continuations and single tokens alike.
+RI_API int ri_attention_prefill_forms(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,
+                                      int max_pages, const int* seq_slot, const int* seq_start, const int* cu_seqlens,
+                                      void* out, int out_ld, int n_seqs, int max_new, int n_heads, int n_kv_heads, int hd,
+                                      int page_size, float scale, int window, float softcap, int keep_first,
+                                      const float* sink, const float* dist, const void* gate, int gate_ld, float out_scale,
+                                      cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads > 65535 || n_seqs > 65535) return fail("attention_prefill: %d heads / %d sequences exceed the grid limit", n_heads, n_seqs);
+    if (window < 0 || keep_first < 0 || softcap < 0.f)
+        return fail("attention_prefill: a window of %d, %d kept positions, a cap of %g", window, keep_first, softcap);
+    ScoreForms f{softcap, keep_first, sink, dist, (const __nv_bfloat16*)gate, gate_ld, out_scale};
+    if (hd == 64)
+        return launch_prefill_forms<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
+                                        max_new, n_heads, n_kv_heads, scale, window, f, out, out_ld, stream);
+    return launch_prefill_forms<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
+                                     max_new, n_heads, n_kv_heads, scale, window, f, out, out_ld, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -3,6 +3,9 @@
   bfloat16, head_dim 64 or 128   one token per sequence: split-K over runs of pages
                                  (`attention_mma`); otherwise the tcgen05 flash-style causal
                                  kernel (`attention_tcgen05`), with the mma.sync one behind it
+  bfloat16, head_dim 64 or 128,  scores with a cap, a bias by distance, kept first positions, a sink or a
+  further forms of the score     gate per head: the mma.sync kernel with those forms (`attention_prefill_forms`),
+                                 for prompts and for single tokens
   anything else                  the generic kernel (`attention_generic`): any head size, any
                                  dtype, float32 arithmetic
 
@@ -30,6 +33,8 @@ def _sm_count() -> int:
 _PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
 # RI_B200_DECODE_ATTENTION=cluster / cp_async / tma forces one of the decode kernels (default: by batch size)
 _DECODE = os.environ.get("RI_B200_DECODE_ATTENTION", "auto")
+# RI_B200_SCORE_FORMS_ATTENTION=generic keeps the generic kernel for scores with a cap, a bias, a sink or a gate
+_FORMS = os.environ.get("RI_B200_SCORE_FORMS_ATTENTION", "mma")
 CLUSTER_SPLITS = 8     # a thread-block cluster holds at most 8 CTAs portably
 
 
@@ -128,6 +133,15 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
             if out_scale != 1.0:
                 ops.scale_(out, out_scale)
             return out
+    if (qkv.dtype == torch.bfloat16 and same_sizes and not chunk and not plain and _FORMS != "generic"
+            and ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, False) and q_ld % 8 == 0
+            and out.shape[1] % 2 == 0):
+        # the forms of the score and the mask on the tensor cores: prompts, continuations and single tokens
+        return ops.attention_prefill_forms(
+            qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens, out,
+            n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+            page_size=ctx.page_size, scale=scale, window=window or 0, softcap=softcap, keep_first=keep_first, sink=sink,
+            dist=dist, gate=gate, out_scale=out_scale)
     return ops.attention_generic(
         qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,

@@ -534,6 +534,33 @@ def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, se
     return out
 
 
+def attention_prefill_forms(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens,
+                            out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int,
+                            head_dim: int, page_size: int, scale: float, window: int = 0, softcap: float = 0.0,
+                            keep_first: int = 0, sink=None, dist=None, gate=None, out_scale: float = 1.0):
+    """bf16 causal attention of every new token of every sequence over its slot's keys on the tensor cores, with the
+    score's cap, the bias by distance (dist float32 [2, heads]), kept first positions beyond the window, a sink
+    (float32 [heads]) and a gate per head (bf16 [tokens, heads], any row stride), each off when zero or None."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens, out, sink, dist, gate)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_prefill_forms: bf16 only")
+    if sink is not None:
+        _f32_vec(sink, n_heads, "attention_prefill_forms: sink")
+    if dist is not None:
+        _f32_vec(dist, 2 * n_heads, "attention_prefill_forms: dist")
+    gate_ld = 0
+    if gate is not None:
+        _need(gate.dtype == torch.bfloat16 and gate.dim() == 2 and gate.shape[1] == n_heads and gate.stride(1) == 1,
+              "attention_prefill_forms: gate must be bf16 [tokens, heads]")
+        gate_ld = gate.stride(0)
+    _call("attention_mma", "ri_attention_prefill_forms", _p(q), c_int(q_ld), _p(kcache), _p(vcache), _p(page_table),
+          c_int(page_table.shape[1]), _p(seq_slot), _p(seq_start), _p(cu_seqlens), _p(out), c_int(out.shape[1]),
+          c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+          c_float(scale), c_int(window), c_float(softcap), c_int(keep_first), _p(sink), _p(dist), _p(gate), c_int(gate_ld),
+          c_float(out_scale), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------
 # A gated linear recurrence with a matrix state per head (csrc/recurrent.cu)
 # ----------------------------------------------------------------------------
