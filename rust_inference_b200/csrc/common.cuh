@@ -113,6 +113,21 @@ __device__ __forceinline__ GateForm load_gate_form(const float* p) {
     return f;
 }
 
+// A learned activation of one argument (epilogue 4 of the contractions, and a kernel of its own):
+//   act(z) = a_p z^2 + z / 2 for z > 0,   a_n (e^z - 1 - z) + z / 2 otherwise,   a_p = softplus(p),  a_n = 1/2 + softplus(q),
+// p and q two floats in device memory.  Continuous at 0 with slope 1/2 on both sides; expm1f keeps e^z - 1 for small z.
+struct ActForm { float ap, an; };
+__device__ __forceinline__ ActForm load_act_form(const float* pq) {
+    const float p = pq[0], q = pq[1];
+    ActForm f;
+    f.ap = p > 20.f ? p : log1pf(expf(p));
+    f.an = 0.5f + (q > 20.f ? q : log1pf(expf(q)));
+    return f;
+}
+__device__ __forceinline__ float act_f32(float z, const ActForm& f) {
+    return z > 0.f ? fmaf(f.ap * z, z, 0.5f * z) : fmaf(f.an, expm1f(z) - z, 0.5f * z);
+}
+
 // The reference's SiLU, stable on both sides (math.rs:137-146).
 __device__ __forceinline__ float silu_f32(float x) {
     if (x >= 0.f) {

@@ -12,6 +12,8 @@
 //                                                      stream, transformer.rs:38-39, :47)
 //   3  out<T>   = silu(acc) * acc2, acc2 = X * W2^T   (SwiGLU, mlp.rs:35-43); `bias`, when not null, points to
 //                                                      the three constants of another gate form (`GateForm`)
+//   4  out<T>   = act(acc)                            a learned activation of one argument (`ActForm`, common.cuh);
+//                                                      `bias` points to its two constants
 #include "common.cuh"
 
 using namespace ri;
@@ -66,6 +68,7 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __re
     const int ty = tid >> 4, tx = tid & 15;
 
     const GateForm gf = load_gate_form(DUAL ? bias : nullptr);
+    const ActForm af = MODE == 4 ? load_act_form(bias) : ActForm{0.f, 0.f};     // the activation's two constants come in `bias`
     float acc[TM][TN];
     float acc2[DUAL ? TM : 1][DUAL ? TN : 1];
 #pragma unroll
@@ -127,8 +130,10 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __re
                 reinterpret_cast<float*>(out_)[o] = v;
             } else if (MODE == 2) {
                 reinterpret_cast<float*>(out_)[o] += v;
-            } else {
+            } else if (MODE == 3) {
                 reinterpret_cast<T*>(out_)[o] = from_f32<T>(gated_f32(v, acc2[i][j], gf));
+            } else {
+                reinterpret_cast<T*>(out_)[o] = from_f32<T>(act_f32(v, af));
             }
         }
     }
@@ -156,6 +161,7 @@ int dispatch_mode(int mode, const void* X, const void* W, const void* W2, const 
         case 1: return launch<T, 1>(X, W, W2, bias, out, M, N, K, stream);
         case 2: return launch<T, 2>(X, W, W2, bias, out, M, N, K, stream);
         case 3: return launch<T, 3>(X, W, W2, bias, out, M, N, K, stream);
+        case 4: return launch<T, 4>(X, W, W2, bias, out, M, N, K, stream);
     }
     return fail("gemm_simt: unknown epilogue mode %d", mode);
 }
@@ -168,6 +174,7 @@ RI_API int ri_gemm_simt(const void* X, const void* W, const void* W2, const floa
     if (K <= 0) return fail("gemm_simt: K must be positive, found %d", K);
     if (mode == 3 && W2 == nullptr) return fail("gemm_simt: the SiLU-gate epilogue needs a second matrix");
     if (mode == 2 && bias != nullptr) return fail("gemm_simt: the residual epilogue takes no bias");
+    if (mode == 4 && bias == nullptr) return fail("gemm_simt: the activation epilogue needs its two constants");
     if (dtype == RI_F32) return dispatch_mode<float>(mode, X, W, W2, bias, out, M, N, K, stream);
     if (dtype == RI_BF16) return dispatch_mode<__nv_bfloat16>(mode, X, W, W2, bias, out, M, N, K, stream);
     return fail("gemm_simt: unknown dtype %d", dtype);

@@ -31,6 +31,8 @@
 //                                                      fed by the same X tile.  This epilogue takes no bias: its
 //                                                      `bias` argument, when not null, points to the three
 //                                                      constants of another gate form (`GateForm`, common.cuh)
+//   4  out<bf16> = act(acc)                           a learned activation of one argument (`ActForm`, common.cuh);
+//                                                      `bias` points to its two constants
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out stores a code in the
 // host-visible status word, the CTA stops issuing work, waits (bounded) for its own
@@ -73,8 +75,11 @@ __device__ __forceinline__ float gated_to_bf16(float g, float u, const GateForm&
 }
 
 template <int MODE>
-__device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2, const GateForm& gf) {
-    if (MODE == 0) {
+__device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2, const GateForm& gf,
+                                             const ActForm& af) {
+    if (MODE == 4) {
+        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(act_f32(acc, af));
+    } else if (MODE == 0) {
         reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + bias);
     } else if (MODE == 1) {
         reinterpret_cast<float*>(out_)[o] = acc + bias;
@@ -286,8 +291,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!landed || abort_flag) break;
             const int f = f0 + lane_base + lane;
             const bool f_ok = f < n_feat;
-            const float b = (MODE != 3 && bias != nullptr && f_ok) ? bias[f] : 0.f;
+            const float b = (MODE != 3 && MODE != 4 && bias != nullptr && f_ok) ? bias[f] : 0.f;
             const GateForm gf = load_gate_form(MODE == 3 ? bias : nullptr);
+            const ActForm af = MODE == 4 ? load_act_form(bias) : ActForm{0.f, 0.f};
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * ACC_COLS);
 #pragma unroll 1
             for (int c0 = 0; c0 < tn; c0 += 16) {
@@ -305,12 +311,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
-                                               DUAL ? __uint_as_float(u[j]) : 0.f, gf);
+                                               DUAL ? __uint_as_float(u[j]) : 0.f, gf, af);
                     } else {
                         for (int j = 0; j < 16; ++j)
                             if (t0 + c0 + j < n_tok)
                                 store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
-                                                   DUAL ? __uint_as_float(u[j]) : 0.f, gf);
+                                                   DUAL ? __uint_as_float(u[j]) : 0.f, gf, af);
                     }
                 }
             }
@@ -355,6 +361,7 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
                                               bool pieces = false) {     // MODE 2: other work items add to the same tile
     constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
     const GateForm gf = load_gate_form(MODE == 3 ? bias : nullptr);     // the gated epilogue's constants come in `bias`
+    const ActForm af = MODE == 4 ? load_act_form(bias) : ActForm{0.f, 0.f};     // so do the activation's
 #pragma unroll 1
     for (int c0 = 0; c0 < FEATS; c0 += 16) {
         if (f0 + c0 >= n_feat) break;                       // uniform over the warp
@@ -370,11 +377,12 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
         for (int j = 0; j < 16; ++j) {
             const float a = __uint_as_float(v[j]);
             if (MODE == 3) r[j] = gated_to_bf16(a, __uint_as_float(u[j]), gf);
+            else if (MODE == 4) r[j] = act_f32(a, af);
             else if (MODE == 2) r[j] = a;
             else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
         }
         if (whole) {
-            if (MODE == 0 || MODE == 3) {
+            if (MODE == 0 || MODE == 3 || MODE == 4) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_) + o0;
                 uint4 lo, hi;
                 lo.x = pack_bf16x2(r[0], r[1]);  lo.y = pack_bf16x2(r[2], r[3]);
@@ -403,7 +411,7 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
         } else {
             for (int j = 0; j < 16; ++j)
                 if (f0 + c0 + j < n_feat) {
-                    if (MODE == 0 || MODE == 3) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
+                    if (MODE == 0 || MODE == 3 || MODE == 4) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
                     else if (MODE == 1) reinterpret_cast<float*>(out_)[o0 + j] = r[j];
                     else if (pieces) atomicAdd(reinterpret_cast<float*>(out_) + o0 + j, r[j]);
                     else reinterpret_cast<float*>(out_)[o0 + j] += r[j];
@@ -1079,7 +1087,8 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
                            int mode, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
     if (n_tok <= 0 || n_feat <= 0) return 0;
     if (K <= 0 || K % 8) return fail("gemm_tcgen05: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
-    if (mode < 0 || mode > 3) return fail("gemm_tcgen05: unknown epilogue mode %d", mode);
+    if (mode < 0 || mode > 4) return fail("gemm_tcgen05: unknown epilogue mode %d", mode);
+    if (mode == 4 && bias == nullptr) return fail("gemm_tcgen05: the activation epilogue needs its two constants");
     if (mode == 3 && map_w2 == nullptr) return fail("gemm_tcgen05: the SiLU-gate epilogue needs a second matrix");
     if (mode == 2 && bias != nullptr) return fail("gemm_tcgen05: the residual epilogue takes no bias");
     if (mode != 2 && split_k > 1) return fail("gemm_tcgen05: only the residual epilogue can split K");
@@ -1097,6 +1106,7 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
             case 0: return launch_pair<false, 0>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
             case 1: return launch_pair<false, 1>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
             case 2: return launch_pair<false, 2>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+            case 4: return launch_pair<false, 4>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
             default: return launch_pair<true, 3>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
         }
     }
@@ -1105,6 +1115,7 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
         case 0: return pick_tile<false, 0>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
         case 1: return pick_tile<false, 1>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
         case 2: return pick_tile<false, 2>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 4: return pick_tile<false, 4>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
         default: return pick_tile<true, 3>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
     }
 }

@@ -122,17 +122,13 @@ __global__ void __launch_bounds__(256) normed_sum_kernel(NormedSum p, float* out
     }
 }
 
-__device__ __forceinline__ float xielu_f32(float z, float ap, float an) {
-    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-}
-
 template <typename T>
 __global__ void xielu_kernel(const T* x, T* out, const float* __restrict__ pq, size_t total) {
     let_next_kernel_start();
-    const float ap = softplus_f32(pq[0]), an = 0.5f + softplus_f32(pq[1]);
+    const ActForm form = load_act_form(pq);
     wait_for_previous_kernels();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-        out[i] = from_f32<T>(xielu_f32(to_f32<T>(x[i]), ap, an));
+        out[i] = from_f32<T>(act_f32(to_f32<T>(x[i]), form));
 }
 
 __global__ void add_row_bias_kernel(float* x, const float* __restrict__ bias, int n, size_t total) {

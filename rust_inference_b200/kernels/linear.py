@@ -64,6 +64,15 @@ def gated(x, w_gate: Weight, w_up: Weight, out, ctx, form=None):
     return ops.gemm_simt(x, w_gate.t, out, ops.EPI_SILU_MUL, w2=w_up.t, gate_form=form)
 
 
+def activated(x, w: Weight, out, ctx, form):
+    """out<run dtype> = act(x W^T), the learned activation of `ops.xielu` with its two constants `form` (float32 [2] on
+    the device), applied to the float32 accumulators in the product's epilogue."""
+    if _use_tensor_cores(x, w):
+        from . import tcgen05
+        return tcgen05.gemm(x, w, out, ops.EPI_ACT, ctx, act_form=form)
+    return ops.gemm_simt(x, w.t, out, ops.EPI_ACT, act_form=form)
+
+
 def accumulate_split(x, w: Weight, acc, ctx) -> bool:
     """acc<float32> += x W^T with K split over enough CTAs to fill the GPU, if the tensor-core
     kernel takes the shape (returns False otherwise and does nothing).  For small steps whose

@@ -321,15 +321,16 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 # epilogues of the contractions
-EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SILU_MUL = 0, 1, 2, 3
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SILU_MUL, EPI_ACT = 0, 1, 2, 3, 4
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
               bias: torch.Tensor | None = None, w2: torch.Tensor | None = None,
-              gate_form: torch.Tensor | None = None) -> torch.Tensor:
+              gate_form: torch.Tensor | None = None, act_form: torch.Tensor | None = None) -> torch.Tensor:
     """out = x @ w.T with the chosen epilogue, on the FFMA pipe (float32 accumulate).  gate_form (gated
     epilogue only): float32 [3] on the device, {alpha, limit, shift} of g' sigmoid(alpha g') (u' + shift) with
-    g' = min(g, limit), u' = clamp(u, -limit, limit); None: SiLU(g) * u."""
+    g' = min(g, limit), u' = clamp(u, -limit, limit); None: SiLU(g) * u.  act_form (EPI_ACT only): float32 [2] on the
+    device, the two constants of the learned activation (`xielu`)."""
     _need_cuda(x, w, out, bias, w2)
     m, k = x.shape
     n = w.shape[0]
@@ -345,6 +346,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
         _need(mode == EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
               and gate_form.numel() == 3, "gemm: a gate form is three float32 constants of the gated epilogue")
         bias = gate_form                      # the gated epilogue takes no bias: its constants travel in that argument
+    _need((mode == EPI_ACT) == (act_form is not None), "gemm: the activation epilogue and its constants go together")
+    if act_form is not None:
+        _need(bias is None and act_form.is_cuda and act_form.dtype == torch.float32 and act_form.numel() == 2,
+              "gemm: an activation's form is two float32 constants, and its epilogue takes no bias")
+        bias = act_form
     _call("gemm_simt", "ri_gemm_simt", _p(x), _p(w), _p(w2), _p(bias), _p(out), c_int(dtype_code(x.dtype)),
           c_int(mode), c_int(m), c_int(n), c_int(k), _stream())
     return out

@@ -117,7 +117,7 @@ def _x_map(x: torch.Tensor, tn: int) -> torch.Tensor:
 
 
 def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, w2=None, split_k: int | None = None,
-         gate_form=None):
+         gate_form=None, act_form=None):
     _need_cuda(x, w.t, out, bias)
     m, k = x.shape
     n = w.n
@@ -136,6 +136,11 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
         _need(mode == ops.EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
               and gate_form.numel() == 3, "gemm_tcgen05: a gate form is three float32 constants of the gated epilogue")
         bias = gate_form
+    _need((mode == ops.EPI_ACT) == (act_form is not None), "gemm_tcgen05: the activation epilogue and its constants go together")
+    if act_form is not None:
+        _need(bias is None and act_form.is_cuda and act_form.dtype == torch.float32 and act_form.numel() == 2,
+              "gemm_tcgen05: an activation's form is two float32 constants, and its epilogue takes no bias")
+        bias = act_form
     if m == 0:
         return out
     tile, planned = plan(m, n, k, mode)

@@ -128,6 +128,9 @@ class GQAttention(Mixer):
             mats += [tensors[nm["k"]]] + ([] if self.values_from_keys else [tensors[nm["v"]]])
         if self.head_gate:
             mats.append(tensors[nm["gate"]])           # one more row per head: the gates come out of the same product
+            rows = sum(m.shape[0] for m in mats)
+            if rows % 8:                               # rows of zeros keep a token's row a multiple of 16 bytes, which the
+                mats.append(torch.zeros(-rows % 8, mats[0].shape[1], dtype=mats[0].dtype, device=mats[0].device))   # tensor-core kernels want
         self.w_qkv = linear.Weight(torch.cat(mats, dim=0))
         if self.sink:
             self.sinks = tensors[nm["sink"]].contiguous()
@@ -140,9 +143,9 @@ class GQAttention(Mixer):
             self.q_norm, self.k_norm = tensors[nm["q_norm"]].contiguous(), tensors[nm["k_norm"]].contiguous()
         if self.qkv_bias:
             biases = [tensors[nm["q_bias"]]] + ([tensors[nm["k_bias"]], tensors[nm["v_bias"]]] if self.own_kv else [])
-            if self.head_gate:
-                biases.append(torch.zeros(self.n_heads, dtype=biases[0].dtype, device=biases[0].device))
             self.b_qkv = torch.cat(biases, dim=0).contiguous()
+            if self.b_qkv.numel() < self.w_qkv.n:      # the gates' rows, and the rows of zeros after them
+                self.b_qkv = torch.cat([self.b_qkv, self.b_qkv.new_zeros(self.w_qkv.n - self.b_qkv.numel())]).contiguous()
         self.w_o = linear.Weight(tensors[nm["o"]])
 
     def get_tensors(self):
@@ -186,7 +189,7 @@ class GQAttention(Mixer):
             raise ValueError("a layer with key and value projections writes its own cache")
         kv_width = (self.kv_dim + (0 if self.values_from_keys else self.v_dim)) if self.own_kv else 0
         gate_col = self.q_dim + kv_width
-        width = gate_col + (self.n_heads if self.head_gate else 0)
+        width = self.w_qkv.n                           # with gates: one more column per head, padded to a multiple of 8
         special = self.values_from_keys or self.qk_norm_eps is not None
         usual = (self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False) and not special
                  and not self.extended)

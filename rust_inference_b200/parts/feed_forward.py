@@ -84,8 +84,8 @@ class BoundedGLU(FeedForward):
 @register("feed_forward", "dense_act")
 class DenseActivation(FeedForward):
     """out = W_down act(W_up x), no gate.  `activation` "xielu": with the two learned numbers p, q of the tensor `act`,
-    act(z) = softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 otherwise (float32
-    arithmetic on the projection's result; p and q are read on the device).  `names`: up, down, act below the prefix."""
+    act(z) = softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 otherwise, applied to
+    the up projection's float32 accumulators in that product's epilogue; p and q are read on the device.  `names`: up, down, act below the prefix."""
 
     _NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "act": "act"}
     ACTIVATIONS = ("xielu",)
@@ -114,6 +114,5 @@ class DenseActivation(FeedForward):
 
     def forward(self, x, residual, ctx):
         act = ctx.buffer("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
-        linear.project(x, self.w_up, act, ctx)
-        ops.xielu(act, act, self.act)
+        linear.activated(x, self.w_up, act, ctx, self.act)
         linear.into_residual(act, self.w_down, residual, ctx)

@@ -146,6 +146,21 @@ def test_learned_activation_kernel(dtype):
     assert float(err.max()) < (3e-6 if dtype == F32 else 5e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,width,ff", [(1, 72, 40), (5, 128, 200), (130, 128, 264), (600, 256, 520), (2100, 512, 1024), (9, 100, 36)])
+def test_activation_in_the_product_s_epilogue(dtype, n, width, ff):
+    """act(x W^T) as one kernel: few and many tokens (every form of the tensor-core kernel), sizes it refuses."""
+    from rust_inference_b200.kernels import linear
+    g = torch.Generator().manual_seed(n + ff)
+    x = torch.randn(n, width, generator=g).to(dtype)
+    w = (torch.randn(ff, width, generator=g) * (2.0 / math.sqrt(width))).to(dtype)
+    pq = torch.tensor([0.4, -0.3])
+    want = plain_redodra.xielu(x.double() @ w.double().T, pq[0].double(), pq[1].double())
+    out = torch.empty(n, ff, dtype=dtype, device=DEV)
+    linear.activated(d(x), linear.Weight(d(w)), out, None, d(pq))
+    assert rel_err(out, want) < (1e-5 if dtype == F32 else 1e-2)
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("groups,size,w_len,gate_first", [(4, 24, 24, False), (1, 72, 72, False), (2, 64, 128, True),
                                                          (3, 40, 120, True), (8, 8, 8, False), (1, 130, 130, True)])
