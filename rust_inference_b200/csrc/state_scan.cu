@@ -119,11 +119,23 @@ __global__ void conv_state_kernel(const float* z, int ld, int conv_col, int conv
 // Threads of a warp: lane = column_in_warp * R + r.  Thread (r, j) keeps ROWS consecutive rows (r * ROWS ...) of
 // column j of the state in registers; sums over the rows are finished by log2(R) shuffles inside the warp.  The
 // tokens' keys, queries, values, decays and steps come through shared memory in tiles, a key's and a query's row
-// slices padded so that the eight slices' 16-byte reads fall into different banks.
+// slices padded so that the eight slices' 16-byte reads fall into different banks.  There are two tiles: while the
+// recurrence runs over one, asynchronous copies (16 bytes each where every column offset and the row length are
+// multiples of four floats, 4 bytes each otherwise) fill the other, so the global loads' latency stays off the
+// sequential path.
 constexpr int R = 8;
 constexpr int SCAN_WARPS = 4;
 constexpr int COLS = SCAN_WARPS * 32 / R;        // value columns per block
 constexpr int SCAN_THREADS = SCAN_WARPS * 32;
+
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 struct Scan {
     const float* u;            // [tokens, ld]: the prepared rows
@@ -135,18 +147,19 @@ struct Scan {
     const int* cu_seqlens;
     const int* seq_slot;
     int heads, groups, dim, vdim, tile_t;
+    int vec;                   // 1: rows, columns and sizes allow 16-byte copies
 };
 
 template <int ROWS, bool DELTA>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
     constexpr int SLICE = ROWS + 4;
     constexpr int TOKEN = 2 * R * SLICE + COLS + 4;       // k, q, the block's values, decay and step
-    extern __shared__ __align__(16) float tile[];
+    extern __shared__ __align__(16) float tile[];          // two tiles of tile_t tokens
     const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
     const int r = threadIdx.x % R, jj = threadIdx.x / R;
     const int j = j0 + jj, i0 = r * ROWS;
     const bool live = j < p.vdim;
-    for (int i = threadIdx.x; i < p.tile_t * TOKEN; i += SCAN_THREADS) tile[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * p.tile_t * TOKEN; i += SCAN_THREADS) tile[i] = 0.f;
     const float skip = p.skip != nullptr ? p.skip[h] : 0.f;
     let_next_kernel_start();
     wait_for_previous_kernels();
@@ -163,22 +176,58 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
     const int o_ld = p.heads * p.vdim;
     __syncthreads();                                      // the zeros are in place
 
-    for (int tb = t0; tb < t1; tb += p.tile_t) {
+    // the copies of the tokens tb .. tb + n_tok - 1 into one of the two tiles; every thread commits one group
+    auto fetch = [&](float* dst, int tb, int n_tok) {
+        if (p.vec) {
+            const int dq = p.dim >> 2, cq = cols >> 2, per = 2 * dq + cq;
+            for (int tok = 0; tok < n_tok; ++tok) {
+                const float* row = p.u + (size_t)(tb + tok) * p.ld;
+                float* base = dst + tok * TOKEN;
+                for (int it = threadIdx.x; it < per; it += SCAN_THREADS) {
+                    if (it < dq) copy_async16(base + (4 * it / ROWS) * SLICE + 4 * it % ROWS, row + k_off + 4 * it);
+                    else if (it < 2 * dq) copy_async16(base + R * SLICE + (4 * (it - dq) / ROWS) * SLICE + 4 * (it - dq) % ROWS, row + q_off + 4 * (it - dq));
+                    else copy_async16(base + 2 * R * SLICE + 4 * (it - 2 * dq), row + v_off + 4 * (it - 2 * dq));
+                }
+            }
+        } else {
+            const int per = 2 * p.dim + cols;
+            for (int tok = 0; tok < n_tok; ++tok) {
+                const float* row = p.u + (size_t)(tb + tok) * p.ld;
+                float* base = dst + tok * TOKEN;
+                for (int it = threadIdx.x; it < per; it += SCAN_THREADS) {
+                    if (it < p.dim) copy_async4(base + (it / ROWS) * SLICE + it % ROWS, row + k_off + it);
+                    else if (it < 2 * p.dim) copy_async4(base + R * SLICE + ((it - p.dim) / ROWS) * SLICE + (it - p.dim) % ROWS, row + q_off + it - p.dim);
+                    else copy_async4(base + 2 * R * SLICE + it - 2 * p.dim, row + v_off + it - 2 * p.dim);
+                }
+            }
+        }
+        for (int tok = threadIdx.x; tok < 2 * n_tok; tok += SCAN_THREADS) {      // decay and step of every token
+            const int tk = tok >> 1, which = tok & 1;
+            copy_async4(dst + tk * TOKEN + 2 * R * SLICE + COLS + which,
+                        p.u + (size_t)(tb + tk) * p.ld + (which ? p.step_col : p.decay_col) + h);
+        }
+        copy_async_commit();
+    };
+
+    const int tile_floats = p.tile_t * TOKEN;
+    fetch(tile, t0, min(p.tile_t, t1 - t0));
+    int buf = 0;
+    for (int tb = t0; tb < t1; tb += p.tile_t, buf ^= 1) {
         const int n_tok = min(p.tile_t, t1 - tb);
-        const int per = 2 * p.dim + cols + 2;
-        for (int idx = threadIdx.x; idx < n_tok * per; idx += SCAN_THREADS) {
-            const int tok = idx / per, it = idx % per;
-            const float* row = p.u + (size_t)(tb + tok) * p.ld;
-            float* base = tile + tok * TOKEN;
-            if (it < p.dim) base[(it / ROWS) * SLICE + it % ROWS] = row[k_off + it];
-            else if (it < 2 * p.dim) base[R * SLICE + ((it - p.dim) / ROWS) * SLICE + (it - p.dim) % ROWS] = row[q_off + it - p.dim];
-            else if (it < 2 * p.dim + cols) base[2 * R * SLICE + it - 2 * p.dim] = row[v_off + it - 2 * p.dim];
-            else if (it == 2 * p.dim + cols) base[2 * R * SLICE + COLS] = row[p.decay_col + h];
-            else base[2 * R * SLICE + COLS + 1] = row[p.step_col + h];
+        const int nb = tb + p.tile_t;
+        if (nb < t1) {                                    // the next tile is on its way while this one is used
+            fetch(tile + (buf ^ 1) * tile_floats, nb, min(p.tile_t, t1 - nb));
+            copy_async_wait<1>();
+        } else {
+            copy_async_wait<0>();
         }
         __syncthreads();
+        const float* cur = tile + buf * tile_floats;
+        // unrolled: only the state's update chains the tokens, so the loads and the read-out's sums of one token overlap
+        // the next token's update
+#pragma unroll(DELTA ? 2 : 4)
         for (int tok = 0; tok < n_tok; ++tok) {
-            const float* base = tile + tok * TOKEN;
+            const float* base = cur + tok * TOKEN;
             const float4* k4 = reinterpret_cast<const float4*>(base + r * SLICE);
             const float4* q4 = reinterpret_cast<const float4*>(base + R * SLICE + r * SLICE);
             const float v = base[2 * R * SLICE + jj];
@@ -218,7 +267,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
             for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && r == 0) p.o[(size_t)(tb + tok) * o_ld + h * p.vdim + j] = fmaf(skip, v, acc);
         }
-        __syncthreads();                                  // the tile may be overwritten
+        __syncthreads();                                  // this tile may be overwritten by the fetch after next
     }
 #pragma unroll
     for (int k = 0; k < ROWS; ++k)
@@ -259,12 +308,12 @@ constexpr int SCAN_SMEM_LIMIT = 44 * 1024;
 template <int ROWS>
 int launch_scan(bool delta, dim3 grid, cudaStream_t stream, Scan p, int longest) {
     const int token_bytes = (2 * R * (ROWS + 4) + COLS + 4) * (int)sizeof(float);
-    int tile_t = SCAN_SMEM_LIMIT / token_bytes;
-    if (tile_t > 32) tile_t = 32;
+    int tile_t = SCAN_SMEM_LIMIT / (2 * token_bytes);     // two tiles
+    if (tile_t > 16) tile_t = 16;
     if (longest > 0 && tile_t > longest) tile_t = longest;
     if (tile_t < 1) tile_t = 1;
     p.tile_t = tile_t;
-    const size_t smem = (size_t)tile_t * token_bytes;
+    const size_t smem = (size_t)2 * tile_t * token_bytes;
     cudaError_t e;
     if (delta) e = launch_dependent(state_scan_kernel<ROWS, true>, grid, SCAN_THREADS, smem, stream, p);
     else e = launch_dependent(state_scan_kernel<ROWS, false>, grid, SCAN_THREADS, smem, stream, p);
@@ -314,7 +363,8 @@ RI_API int ri_state_scan(const float* u, int ld, int q_col, int k_col, int v_col
     if (dim > 32 * R) return fail("state_scan: a state of %d rows exceeds %d", dim, 32 * R);
     int rows = (dim + R - 1) / R;
     rows = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
-    Scan p{u, ld, q_col, k_col, v_col, decay_col, step_col, skip, state, o, cu_seqlens, seq_slot, heads, groups, dim, vdim, 1};
+    const int vec = ((ld | q_col | k_col | v_col | dim | vdim) % 4 == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0) ? 1 : 0;
+    Scan p{u, ld, q_col, k_col, v_col, decay_col, step_col, skip, state, o, cu_seqlens, seq_slot, heads, groups, dim, vdim, 1, vec};
     dim3 grid(n_seqs, heads, (vdim + COLS - 1) / COLS);
     if (rows == 4) return launch_scan<4>(delta != 0, grid, stream, p, longest_run);
     if (rows == 8) return launch_scan<8>(delta != 0, grid, stream, p, longest_run);

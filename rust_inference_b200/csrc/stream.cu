@@ -18,6 +18,7 @@
 // All arithmetic is float32 with accurate tanhf / expf / expm1f.  Data an earlier kernel of the step wrote is read
 // after `wait_for_previous_kernels()` through plain pointers.
 #include "common.cuh"
+#include <initializer_list>
 
 using namespace ri;
 
@@ -25,17 +26,64 @@ namespace {
 
 __device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-template <typename T>
-__global__ void dyt_norm_kernel(const float* x, const float* __restrict__ w, const float* __restrict__ b,
+// V consecutive floats of a row as one access (V = 4: 16 bytes; rows and pointers must allow it) or one by one.
+template <int V> struct Pack { float v[V]; };
+template <int V> __device__ __forceinline__ Pack<V> load_pack(const float* p) {
+    Pack<V> r;
+    if constexpr (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) r.v[k] = p[k];
+    }
+    return r;
+}
+template <int V> __device__ __forceinline__ Pack<V> zero_pack() {
+    Pack<V> r;
+#pragma unroll
+    for (int k = 0; k < V; ++k) r.v[k] = 0.f;
+    return r;
+}
+template <int V> __device__ __forceinline__ void store_pack(float* p, const Pack<V>& r) {
+    if constexpr (V == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) p[k] = r.v[k];
+    }
+}
+template <int V> __device__ __forceinline__ void store_pack(__nv_bfloat16* p, const Pack<V>& r) {
+    if constexpr (V == 4) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&lo);
+        u.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) p[k] = __float2bfloat16_rn(r.v[k]);
+    }
+}
+
+// A thread owns V columns and walks down the rows (blockIdx.y, then in steps of gridDim.y): the vectors of its columns
+// are read once, and no index is ever divided.
+template <typename T, int V>
+__global__ void __launch_bounds__(128) dyt_norm_kernel(const float* x, const float* __restrict__ w, const float* __restrict__ b,
                                 const float* __restrict__ alpha, const int* rows, T* __restrict__ out, int n_rows, int n) {
     let_next_kernel_start();
     const float a = alpha[0];
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    const bool mine = c < n;
+    const Pack<V> wv = mine ? load_pack<V>(w + c) : zero_pack<V>(), bv = mine ? load_pack<V>(b + c) : zero_pack<V>();
     wait_for_previous_kernels();
-    const size_t total = (size_t)n_rows * n;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int r = (int)(i / n), c = (int)(i % n);
+    if (!mine) return;
+    for (int r = blockIdx.y; r < n_rows; r += gridDim.y) {
         const int src = rows != nullptr ? rows[r] : r;
-        out[i] = from_f32<T>(fmaf(tanhf(a * x[(size_t)src * n + c]), w[c], b[c]));
+        Pack<V> v = load_pack<V>(x + (size_t)src * n + c);
+#pragma unroll
+        for (int k = 0; k < V; ++k) v.v[k] = fmaf(tanhf(a * v.v[k]), wv.v[k], bv.v[k]);
+        store_pack<V>(out + (size_t)r * n + c, v);
     }
 }
 
@@ -57,32 +105,52 @@ struct StreamUpdate {
     int n_tokens, n;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) stream_update_kernel(StreamUpdate p) {
+template <typename T, int V>
+__global__ void __launch_bounds__(128) stream_update_kernel(StreamUpdate p) {
     let_next_kernel_start();
     const float pa = p.post_w != nullptr ? p.post_alpha[0] : 0.f;
     const float na = p.next_w != nullptr ? p.next_alpha[0] : 0.f;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    const bool mine = c < p.n;
+    const bool post = p.post_w != nullptr && mine, next = p.next_w != nullptr && mine;
+    const Pack<V> bias = (p.branch_bias != nullptr && mine) ? load_pack<V>(p.branch_bias + c) : zero_pack<V>();
+    const Pack<V> pw = post ? load_pack<V>(p.post_w + c) : zero_pack<V>(), pb = post ? load_pack<V>(p.post_b + c) : zero_pack<V>();
+    const Pack<V> nw = next ? load_pack<V>(p.next_w + c) : zero_pack<V>(), nb = next ? load_pack<V>(p.next_b + c) : zero_pack<V>();
     wait_for_previous_kernels();
+    if (!mine) return;
     const size_t total = (size_t)p.n_tokens * p.n;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % p.n);
-        float r = p.stream[i];
+    const int last = p.depth_index + 1;
+    for (int row = blockIdx.y; row < p.n_tokens; row += gridDim.y) {
+        const size_t i = (size_t)row * p.n + c;
+        Pack<V> r = load_pack<V>(p.stream + i);
         if (p.branch != nullptr) {
-            float v = p.branch[i];
-            p.branch[i] = 0.f;
-            if (p.branch_bias != nullptr) v += p.branch_bias[c];
-            r += p.post_w != nullptr ? fmaf(tanhf(pa * v), p.post_w[c], p.post_b[c]) : v;
+            const Pack<V> v = load_pack<V>(p.branch + i);
+            store_pack<V>(p.branch + i, zero_pack<V>());
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const float x = v.v[k] + bias.v[k];
+                r.v[k] += p.post_w != nullptr ? fmaf(tanhf(pa * x), pw.v[k], pb.v[k]) : x;
+            }
         }
         if (p.history != nullptr) {
-            const int last = p.depth_index + 1;
-            if (p.store_result) p.history[(size_t)last * total + i] = r;
-            float acc = 0.f;
-            for (int j = 0; j < last; ++j) acc = fmaf(p.depth_w[j], p.history[(size_t)j * total + i], acc);
-            r = fmaf(p.depth_w[last], r, acc);
+            if (p.store_result) store_pack<V>(p.history + (size_t)last * total + i, r);
+            Pack<V> acc = zero_pack<V>();
+            for (int j = 0; j < last; ++j) {
+                const float wj = p.depth_w[j];
+                const Pack<V> hj = load_pack<V>(p.history + (size_t)j * total + i);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc.v[k] = fmaf(wj, hj.v[k], acc.v[k]);
+            }
+            const float wl = p.depth_w[last];
+#pragma unroll
+            for (int k = 0; k < V; ++k) r.v[k] = fmaf(wl, r.v[k], acc.v[k]);
         }
-        p.stream[i] = r;
-        if (p.next_w != nullptr)
-            reinterpret_cast<T*>(p.next_out)[i] = from_f32<T>(fmaf(tanhf(na * r), p.next_w[c], p.next_b[c]));
+        store_pack<V>(p.stream + i, r);
+        if (p.next_w != nullptr) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) r.v[k] = fmaf(tanhf(na * r.v[k]), nw.v[k], nb.v[k]);
+            store_pack<V>(reinterpret_cast<T*>(p.next_out) + i, r);
+        }
     }
 }
 
@@ -96,6 +164,8 @@ struct NormedSum {
 };
 
 // A block per row; the row of every member is read twice (sum of squares, then the weighted values): it stays in L1.
+// V = 4: 16-byte accesses where the rows and pointers allow them.
+template <int V>
 __global__ void __launch_bounds__(256) normed_sum_kernel(NormedSum p, float* out, int n, float eps, int accumulate) {
     __shared__ float scratch[33];
     let_next_kernel_start();
@@ -104,21 +174,29 @@ __global__ void __launch_bounds__(256) normed_sum_kernel(NormedSum p, float* out
     float inv[MAX_MEMBERS];
     for (int m = 0; m < p.members; ++m) {
         float ss = 0.f;
-        for (int c = threadIdx.x; c < n; c += blockDim.x) {
-            const float v = p.x[m][row + c] + (p.bias[m] != nullptr ? p.bias[m][c] : 0.f);
-            ss = fmaf(v, v, ss);
+        for (int c = threadIdx.x * V; c < n; c += blockDim.x * V) {
+            const Pack<V> x = load_pack<V>(p.x[m] + row + c);
+            const Pack<V> bv = p.bias[m] != nullptr ? load_pack<V>(p.bias[m] + c) : zero_pack<V>();
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const float v = x.v[k] + bv.v[k];
+                ss = fmaf(v, v, ss);
+            }
         }
         ss = block_sum(ss, scratch);
         inv[m] = p.scale[m] / sqrtf(ss / (float)n + eps);
     }
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        float acc = accumulate ? out[row + c] : 0.f;
+    for (int c = threadIdx.x * V; c < n; c += blockDim.x * V) {
+        Pack<V> acc = accumulate ? load_pack<V>(out + row + c) : zero_pack<V>();
         for (int m = 0; m < p.members; ++m) {
-            const float v = p.x[m][row + c] + (p.bias[m] != nullptr ? p.bias[m][c] : 0.f);
-            p.x[m][row + c] = 0.f;
-            acc = fmaf(v * inv[m], p.w[m][c], acc);
+            const Pack<V> x = load_pack<V>(p.x[m] + row + c);
+            const Pack<V> bv = p.bias[m] != nullptr ? load_pack<V>(p.bias[m] + c) : zero_pack<V>();
+            const Pack<V> wv = load_pack<V>(p.w[m] + c);
+            store_pack<V>(p.x[m] + row + c, zero_pack<V>());
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc.v[k] = fmaf((x.v[k] + bv.v[k]) * inv[m], wv.v[k], acc.v[k]);
         }
-        out[row + c] = acc;
+        store_pack<V>(out + row + c, acc);
     }
 }
 
@@ -138,6 +216,22 @@ __global__ void add_row_bias_kernel(float* x, const float* __restrict__ bias, in
         x[i] += bias[i % n];
 }
 
+// Whether every pointer given lies on a 16-byte boundary (null counts) and rows of n floats keep it.
+inline bool rows_of_16_bytes(int n, std::initializer_list<const void*> ptrs) {
+    if (n % 4) return false;
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) & 15) return false;
+    return true;
+}
+
+// The grid of a kernel whose threads own V columns and walk down the rows.
+inline dim3 column_grid(int n_rows, int n, int v, int threads) {
+    const int gx = (n / v + threads - 1) / threads;
+    int gy = 148 * 8 / gx;
+    gy = gy < 1 ? 1 : (gy > n_rows ? n_rows : gy);
+    return dim3(gx, gy);
+}
+
 inline int blocks_for(size_t total, int threads) {
     const size_t b = (total + threads - 1) / threads;
     return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -148,13 +242,15 @@ inline int blocks_for(size_t total, int threads) {
 RI_API int ri_dyt_norm(const float* x, const float* w, const float* b, const float* alpha, const int* rows, void* out,
                        int out_dtype, int n_rows, int n, cudaStream_t stream) {
     if (n_rows <= 0 || n <= 0) return 0;
-    const size_t total = (size_t)n_rows * n;
+    const bool vec = rows_of_16_bytes(n, {x, w, b, out});
+    const dim3 grid = column_grid(n_rows, n, vec ? 4 : 1, 128);
     cudaError_t e;
     if (out_dtype == RI_F32)
-        e = launch_dependent(dyt_norm_kernel<float>, blocks_for(total, 256), 256, 0, stream, x, w, b, alpha, rows, (float*)out, n_rows, n);
+        e = vec ? launch_dependent(dyt_norm_kernel<float, 4>, grid, 128, 0, stream, x, w, b, alpha, rows, (float*)out, n_rows, n)
+                : launch_dependent(dyt_norm_kernel<float, 1>, grid, 128, 0, stream, x, w, b, alpha, rows, (float*)out, n_rows, n);
     else if (out_dtype == RI_BF16)
-        e = launch_dependent(dyt_norm_kernel<__nv_bfloat16>, blocks_for(total, 256), 256, 0, stream, x, w, b, alpha, rows,
-                             (__nv_bfloat16*)out, n_rows, n);
+        e = vec ? launch_dependent(dyt_norm_kernel<__nv_bfloat16, 4>, grid, 128, 0, stream, x, w, b, alpha, rows, (__nv_bfloat16*)out, n_rows, n)
+                : launch_dependent(dyt_norm_kernel<__nv_bfloat16, 1>, grid, 128, 0, stream, x, w, b, alpha, rows, (__nv_bfloat16*)out, n_rows, n);
     else
         return fail("dyt_norm: unknown dtype %d", out_dtype);
     return check_launch(e, "dyt_norm");
@@ -170,12 +266,15 @@ RI_API int ri_stream_update(float* stream_x, float* branch, const float* branch_
     if (next_w != nullptr && (next_b == nullptr || next_alpha == nullptr || next_out == nullptr)) return fail("stream_update: the norm of the new stream is incomplete");
     StreamUpdate p{stream_x, branch, branch_bias, post_w, post_b, post_alpha, history, depth_w, depth_index, store_result,
                    next_w, next_b, next_alpha, next_out, n_tokens, n};
-    const size_t total = (size_t)n_tokens * n;
+    const bool vec = rows_of_16_bytes(n, {stream_x, branch, branch_bias, post_w, post_b, history, next_w, next_b, next_out});
+    const dim3 grid = column_grid(n_tokens, n, vec ? 4 : 1, 128);
     cudaError_t e;
     if (next_w == nullptr || next_dtype == RI_F32)
-        e = launch_dependent(stream_update_kernel<float>, blocks_for(total, 256), 256, 0, stream, p);
+        e = vec ? launch_dependent(stream_update_kernel<float, 4>, grid, 128, 0, stream, p)
+                : launch_dependent(stream_update_kernel<float, 1>, grid, 128, 0, stream, p);
     else if (next_dtype == RI_BF16)
-        e = launch_dependent(stream_update_kernel<__nv_bfloat16>, blocks_for(total, 256), 256, 0, stream, p);
+        e = vec ? launch_dependent(stream_update_kernel<__nv_bfloat16, 4>, grid, 128, 0, stream, p)
+                : launch_dependent(stream_update_kernel<__nv_bfloat16, 1>, grid, 128, 0, stream, p);
     else
         return fail("stream_update: unknown dtype %d", next_dtype);
     return check_launch(e, "stream_update");
@@ -193,7 +292,10 @@ RI_API int ri_normed_sum(float* const* xs, const float* const* biases, const flo
         p.w[m] = ws[m];
         p.scale[m] = scales[m];
     }
-    cudaError_t e = launch_dependent(normed_sum_kernel, n_tokens, 256, 0, stream, p, out, n, eps, accumulate);
+    bool vec = rows_of_16_bytes(n, {out});
+    for (int m = 0; m < members; ++m) vec = vec && rows_of_16_bytes(n, {xs[m], biases[m], ws[m]});
+    cudaError_t e = vec ? launch_dependent(normed_sum_kernel<4>, n_tokens, 256, 0, stream, p, out, n, eps, accumulate)
+                        : launch_dependent(normed_sum_kernel<1>, n_tokens, 256, 0, stream, p, out, n, eps, accumulate);
     return check_launch(e, "normed_sum");
 }
 
