@@ -965,6 +965,198 @@ attn_prefill_forms_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const _
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode with those forms: one token per sequence.  As attn_decode, a CTA serves one (sequence, kv head, split) with
+// the query heads that share the kv head as the rows of the MMA, its warps take 16 keys of each page each, and the
+// splits' partial results are merged by attn_combine.  The pages walked are those of the kept first positions that
+// lie before the window's first page, then the window's.  The sink enters the first split's statistics as one more
+// key with no value; the gate and the factor on the result scale a split's unnormalised outputs, not its sum, so the
+// merge needs to know neither.
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_forms_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
+                         const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
+                         const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
+                         const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale, int window,
+                         ScoreForms f, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, int out_ld) {
+    constexpr int TILE = PAGE * HD * 2;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t kv_base = smem_u32(smem);              // [NBUF buffers][K tile, V tile], then the Q tile [16][HD]
+    const uint32_t q_tile = kv_base + 2 * NBUF * TILE;
+
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int n_rep = n_heads / n_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    // the two rows of this thread are the heads h0 + g and h0 + g + 8 (rows past n_rep are zero queries)
+    const int h0 = kvh * n_rep;
+    const int hr[2] = {h0 + min(g, n_rep - 1), h0 + min(g + 8, n_rep - 1)};
+    float r1[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f}, sink[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        if (f.dist != nullptr) { r1[half] = f.dist[hr[half]]; r2[half] = f.dist[n_heads + hr[half]]; }
+        if (f.sink != nullptr) sink[half] = f.sink[hr[half]];
+    }
+    const float inv_cap = f.softcap > 0.f ? 1.f / f.softcap : 0.f;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // q, the gates and the newest key and value come from the kernels before
+    const int n_keys = seq_len[b];        // counts the new token, whose key is in the cache by then
+    const int pos = n_keys - 1;
+    const int token = cu_seqlens[b];
+    const int first_key = first_visible_key(pos, window);
+    const int keep = window > 0 ? f.keep_first : 0;
+    const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
+
+    const int pg_lo = first_key / PAGE, pg_hi = (n_keys + PAGE - 1) / PAGE;
+    const int kept_pages = min(pg_lo, (keep + PAGE - 1) / PAGE);
+    const int all_pages = kept_pages + pg_hi - pg_lo;
+    const int per = (all_pages + n_splits - 1) / n_splits;
+    const int i_begin = split * per, i_end = min(all_pages, i_begin + per);
+    const int n_pages = max(0, i_end - i_begin);
+    auto page_of = [&](int i) { return i < kept_pages ? i : pg_lo + i - kept_pages; };
+
+    auto issue = [&](int i, int buf) {
+        int page = pages[page_of(i)];
+        if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;
+        const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * HD;
+        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
+        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
+        cp_async_commit();
+    };
+    int issued = 0;
+    while (issued < n_pages && issued < NBUF) {
+        issue(i_begin + issued, issued);
+        ++issued;
+    }
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)token * q_ld + (size_t)(h0 + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(smem + 2 * NBUF * TILE + tile_off<HD>(r, c)) = v;
+    }
+    __syncthreads();
+
+    uint32_t qf[HD / 16][4];
+    {
+        const int row = lane & 15, half = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(q_tile + tile_off<HD>(row, ks * 2 + half), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+    for (int i = 0; i < n_pages; ++i) {
+        const int buf = i % NBUF;
+        while (issued < n_pages && issued <= i + NBUF - 1) {
+            issue(i_begin + issued, issued % NBUF);
+            ++issued;
+        }
+        const int behind = issued - i - 1;
+        if (behind >= 2) cp_async_wait<2>(); else if (behind == 1) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();
+        const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
+        const int kbase = warp * 16;
+        const int key0 = page_of(i_begin + i) * PAGE + kbase;
+        if (key0 < n_keys && (key0 + 16 > first_key || key0 < keep)) {
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            qk_16keys<HD>(qf, ktile, kbase, s);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + t * 8 + 2 * tq + (e & 1);
+                    const int half = e >> 1;
+                    const bool vis = key < n_keys && (key >= first_key || key < keep);
+                    float v = s[t][e] * scale;
+                    if (f.softcap > 0.f) v = f.softcap * tanhf(v * inv_cap);
+                    if (f.dist != nullptr) v -= r1[half] * log1pf(r2[half] * (float)max(pos - key, 0));
+                    s[t][e] = vis ? v : -INFINITY;
+                }
+            softmax_update<2, HD / 8>(s, m, l, o);
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float a = s[c >> 1][2 * (c & 1)], bb = s[c >> 1][2 * (c & 1) + 1];
+                const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(bb);
+                hi[c] = pack_bf16(a, bb);
+                lo[c] = pack_bf16(a - __bfloat162float(ah), bb - __bfloat162float(bh));
+            }
+            pv_16keys<HD>(hi, vtile, kbase, o);
+            pv_16keys<HD>(lo, vtile, kbase, o);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float factor = f.out_scale;
+        if (f.sink != nullptr && split == 0 && warp == 0) {        // once per row: one more key, with no value
+            const float m_new = fmaxf(m[half], sink[half]);
+            const float alpha = expf(m[half] - m_new);             // m = -inf gives 0
+            l[half] = l[half] * alpha + expf(sink[half] - m_new);
+            m[half] = m_new;
+            factor *= alpha;
+        }
+        if (f.gate != nullptr) {
+            const float gv = __bfloat162float(f.gate[(size_t)token * f.gate_ld + hr[half]]);
+            factor *= gv >= 0.f ? 1.f / (1.f + expf(-gv)) : expf(gv) / (1.f + expf(gv));
+        }
+#pragma unroll
+        for (int t = 0; t < HD / 8; ++t) {
+            o[t][2 * half] *= factor;
+            o[t][2 * half + 1] *= factor;
+        }
+    }
+    constexpr int SO_LD = HD + 4;
+    float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD], over the page buffers
+    float* sml = so + 4 * 16 * SO_LD;                     // [4][16][2]
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) {
+        const int d = t * 8 + 2 * tq;
+        *reinterpret_cast<float2*>(so + (warp * 16 + g) * SO_LD + d) = make_float2(o[t][0], o[t][1]);
+        *reinterpret_cast<float2*>(so + (warp * 16 + g + 8) * SO_LD + d) = make_float2(o[t][2], o[t][3]);
+    }
+    if (tq == 0) {
+        sml[((warp * 16 + g) << 1)] = m[0];
+        sml[((warp * 16 + g) << 1) + 1] = l[0];
+        sml[((warp * 16 + g + 8) << 1)] = m[1];
+        sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
+    }
+    __syncthreads();
+    for (int it = threadIdx.x; it < n_rep * (HD / 4); it += THREADS) {
+        const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
+        write_merged<HD>(so, sml, r, d, b, h0 + r, token, n_heads, n_splits, split, part_o, part_ml, out, out_ld);
+    }
+}
+
+template <int HD>
+int launch_decode_forms(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
+                        const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
+                        int n_kv_heads, float scale, int window, ScoreForms f, int n_splits, float* part_o, float* part_ml,
+                        void* out, int out_ld, cudaStream_t stream) {
+    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // the merge area lies over the page buffers
+    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2) * 4 <= SMEM, "merge area must fit");
+    static PerDeviceOnce configured;
+    if (int rc = raise_dynamic_smem(attn_decode_forms_kernel<HD>, SMEM, configured, "attention")) return rc;
+    dim3 grid(n_seqs, n_kv_heads, n_splits);
+    cudaError_t e = launch_dependent(
+        attn_decode_forms_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
+        n_heads, n_kv_heads, scale, window, f, n_splits, part_o, part_ml, (__nv_bfloat16*)out, out_ld);
+    if (int rc = check_launch(e, "attn_decode_forms")) return rc;
+    if (n_splits > 1) {
+        e = launch_dependent(attn_combine_kernel, dim3(n_seqs, n_heads), dim3(HD >= 128 ? 128 : 64), (size_t)0, stream,
+                             (const float*)part_o, (const float*)part_ml, cu_seqlens, n_heads, (int)HD, n_splits,
+                             (__nv_bfloat16*)out, out_ld);
+        return check_launch(e, "attn_combine");
+    }
+    return 0;
+}
+
 template <int HD>
 int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
                   const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
@@ -1231,6 +1423,30 @@ RI_API int ri_attention_prefill_forms(const void* q, int q_ld, const void* kcach
                                         max_new, n_heads, n_kv_heads, scale, window, f, out, out_ld, stream);
     return launch_prefill_forms<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
                                      max_new, n_heads, n_kv_heads, scale, window, f, out, out_ld, stream);
+}
+
+// One token per sequence with those forms, the sequence's pages cut into n_splits runs (scratch as for
+// ri_attention_decode; it may be null when n_splits == 1).
+RI_API int ri_attention_decode_forms(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,
+                                     int max_pages, const int* seq_slot, const int* seq_len, const int* cu_seqlens,
+                                     void* out, int out_ld, int n_seqs, int n_heads, int n_kv_heads, int hd, int page_size,
+                                     float scale, int window, float softcap, int keep_first, const float* sink,
+                                     const float* dist, const void* gate, int gate_ld, float out_scale, int n_splits,
+                                     float* part_o, float* part_ml, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
+    if (n_splits < 1 || n_splits > 65535) return fail("attention_decode: %d splits", n_splits);
+    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return fail("attention_decode: splits need scratch");
+    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
+    if (window < 0 || keep_first < 0 || softcap < 0.f)
+        return fail("attention_decode: a window of %d, %d kept positions, a cap of %g", window, keep_first, softcap);
+    ScoreForms f{softcap, keep_first, sink, dist, (const __nv_bfloat16*)gate, gate_ld, out_scale};
+    if (hd == 64)
+        return launch_decode_forms<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                                       n_heads, n_kv_heads, scale, window, f, n_splits, part_o, part_ml, out, out_ld, stream);
+    return launch_decode_forms<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                                    n_heads, n_kv_heads, scale, window, f, n_splits, part_o, part_ml, out, out_ld, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

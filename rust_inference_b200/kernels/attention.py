@@ -33,7 +33,8 @@ def _sm_count() -> int:
 _PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
 # RI_B200_DECODE_ATTENTION=cluster / cp_async / tma forces one of the decode kernels (default: by batch size)
 _DECODE = os.environ.get("RI_B200_DECODE_ATTENTION", "auto")
-# RI_B200_SCORE_FORMS_ATTENTION=generic keeps the generic kernel for scores with a cap, a bias, a sink or a gate
+# RI_B200_SCORE_FORMS_ATTENTION=generic keeps the generic kernel for scores with a cap, a bias, a sink or a gate;
+# =prefill keeps the prompts' kernel for steps of one token per sequence too
 _FORMS = os.environ.get("RI_B200_SCORE_FORMS_ATTENTION", "mma")
 CLUSTER_SPLITS = 8     # a thread-block cluster holds at most 8 CTAs portably
 
@@ -136,7 +137,23 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
     if (qkv.dtype == torch.bfloat16 and same_sizes and not chunk and not plain and _FORMS != "generic"
             and ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, False) and q_ld % 8 == 0
             and out.shape[1] % 2 == 0):
-        # the forms of the score and the mask on the tensor cores: prompts, continuations and single tokens
+        # the forms of the score and the mask on the tensor cores
+        if ctx.all_single and n_heads // n_kv_heads <= 16 and _FORMS != "prefill":
+            # one token per sequence: the heads of a kv head are one CTA's rows, the sequence's pages cut into runs
+            longest = ctx.page_table.shape[1] * ctx.page_size
+            if window:
+                longest = min(longest, window + keep_first + 2 * ctx.page_size)
+            splits = decode_splits(ctx.n_seqs, n_kv_heads, longest, ctx.page_size)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = ctx.buffer("attn_forms_part_o", (ctx.n_seqs * n_heads * splits * head_dim,), torch.float32)
+                part_ml = ctx.buffer("attn_forms_part_ml", (ctx.n_seqs * n_heads * splits * 2,), torch.float32)
+            return ops.attention_decode_forms(
+                qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_len, ctx.cu_seqlens, out,
+                n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
+                scale=scale, window=window or 0, softcap=softcap, keep_first=keep_first, sink=sink, dist=dist, gate=gate,
+                out_scale=out_scale, n_splits=splits, part_o=part_o, part_ml=part_ml)
+        # prompts and continuations (and single tokens, if asked for)
         return ops.attention_prefill_forms(
             qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens, out,
             n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,

@@ -567,6 +567,37 @@ def attention_prefill_forms(q: torch.Tensor, q_ld: int, kcache, vcache, page_tab
     return out
 
 
+def attention_decode_forms(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens,
+                           out: torch.Tensor, *, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                           scale: float, window: int = 0, softcap: float = 0.0, keep_first: int = 0, sink=None, dist=None,
+                           gate=None, out_scale: float = 1.0, n_splits: int = 1, part_o=None, part_ml=None):
+    """The same forms for a step of one token per sequence: a CTA per (sequence, kv head, run of pages), the runs'
+    partial results (float32 scratch part_o [seqs * heads * splits * head_dim], part_ml [seqs * heads * splits * 2])
+    merged by a second kernel when n_splits > 1."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens, out, sink, dist, gate, part_o, part_ml)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_decode_forms: bf16 only")
+    if sink is not None:
+        _f32_vec(sink, n_heads, "attention_decode_forms: sink")
+    if dist is not None:
+        _f32_vec(dist, 2 * n_heads, "attention_decode_forms: dist")
+    gate_ld = 0
+    if gate is not None:
+        _need(gate.dtype == torch.bfloat16 and gate.dim() == 2 and gate.shape[1] == n_heads and gate.stride(1) == 1,
+              "attention_decode_forms: gate must be bf16 [tokens, heads]")
+        gate_ld = gate.stride(0)
+    if n_splits > 1:
+        _need(part_o is not None and part_ml is not None and part_o.dtype == torch.float32 and part_ml.dtype == torch.float32
+              and part_o.numel() >= n_seqs * n_heads * n_splits * head_dim and part_ml.numel() >= n_seqs * n_heads * n_splits * 2,
+              "attention_decode_forms: scratch for the runs' partial results")
+    _call("attention_mma", "ri_attention_decode_forms", _p(q), c_int(q_ld), _p(kcache), _p(vcache), _p(page_table),
+          c_int(page_table.shape[1]), _p(seq_slot), _p(seq_len), _p(cu_seqlens), _p(out), c_int(out.shape[1]),
+          c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
+          c_float(softcap), c_int(keep_first), _p(sink), _p(dist), _p(gate), c_int(gate_ld), c_float(out_scale),
+          c_int(n_splits), _p(part_o), _p(part_ml), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------
 # A gated linear recurrence with a matrix state per head (csrc/recurrent.cu)
 # ----------------------------------------------------------------------------

@@ -732,3 +732,52 @@ def test_tensor_core_kernel_takes_the_forms_of_the_score(kind, dim, monkeypatch)
     monkeypatch.setattr(ops, "attention_generic", refuse)
     ws = Workspace(DEV)
     assert rel_err(_drive(part, cache, x, [150, 1], dtype, ws), want) < 3e-2
+
+
+@pytest.mark.parametrize("kind,dim,heads,kv", [("gated", 64, 8, 2), ("gated", 128, 4, 4), ("window", 64, 6, 2), ("window", 128, 16, 1)])
+@pytest.mark.parametrize("splits", [None, "1", "3"])
+def test_single_tokens_with_forms_of_the_score_in_runs_of_pages(kind, dim, heads, kv, splits, monkeypatch):
+    """Steps of one token per sequence with a cap, a bias, kept positions, a sink or a gate: the heads of a kv head are
+    one CTA's rows and the pages are cut into runs (one run, a few, as many as the GPU holds: some stay empty).  Kept
+    positions fill more than one page and lie pages before the window; a query whose key is the far one stands out."""
+    from rust_inference_b200.cache.sequence_cache import SequenceCache
+    from rust_inference_b200.engine.context import Workspace
+    from rust_inference_b200.kernels import ops, attention as attn_kernels
+
+    def refuse(*a, **k):
+        raise AssertionError("another attention kernel was called for a step of single tokens")
+    width, n, first, dtype = 128, 460, 430, torch.bfloat16
+    if kind == "gated":
+        m = redodra_models.attn(heads=heads, kv=kv, dim=dim, vdim=dim, scale=0.9 / math.sqrt(dim), cap=11.0, base=5000.0, rot=32)
+    else:
+        m = redodra_models.window(heads=heads, kv=kv, dim=dim, vdim=dim, scale=0.7 / math.sqrt(dim), cap=6.0, size=150, keep=70)
+    part, W, p = _mixer(kind, m, dtype, width, seed=dim + heads, hot=1.5)
+    cache = SequenceCache([part.cache_request()], max_tokens=2048, max_seq_len=1024, dtype=dtype, device=DEV, n_slots=2)
+    x = (torch.randn(n, width, generator=torch.Generator().manual_seed(heads)) * 0.3).to(dtype)
+    x[n - 7] = x[3] * 4                    # a late query that resembles an early key (a kept position, far before the window)
+    h = x.double()
+    want = (plain_redodra.gated_attention(h, W, p, m, plain_redodra.gated_attention_keys(h, W, p, m)) if kind == "gated"
+            else plain_redodra.windowed_attention(h, W, p, m))
+    if splits is not None:
+        monkeypatch.setenv("RI_B200_DECODE_SPLITS", splits)
+    ws = Workspace(DEV)
+    whole = _drive(part, cache, x, [n], dtype, ws)
+    monkeypatch.setattr(ops, "attention_generic", refuse)
+    prefill = ops.attention_prefill_forms
+    calls = []
+
+    def prompts_only(q, *a, **k):
+        assert q.shape[0] > 1, "the prompts' kernel was called for a step of single tokens"
+        return prefill(q, *a, **k)
+    decode = ops.attention_decode_forms
+
+    def counted(*a, **k):
+        calls.append(k["n_splits"])
+        return decode(*a, **k)
+    monkeypatch.setattr(ops, "attention_prefill_forms", prompts_only)
+    monkeypatch.setattr(ops, "attention_decode_forms", counted)
+    got = _drive(part, cache, x, [first, 1], dtype, ws)
+    assert len(calls) == n - first and (splits is None or set(calls) == {int(splits)})
+    assert rel_err(got, want) < 3e-2 and rel_err(whole, want) < 3e-2
+    assert rel_err(got[first:], want[first:]) < 3e-2
+    assert rel_err(got[first:], whole[first:]) < 2e-2
