@@ -802,7 +802,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
 // ---------------------------------------------------------------------------------------------
 // prefill / continuation / decode with further forms of the score, the mask and the result (the generic
 // kernel's, see attention_generic.cu), 64 query tokens of one head per CTA as above:
-//   softcap     s <- softcap * tanh(s / softcap) after the scale (accurate tanhf)
+//   softcap     s <- softcap * tanh(s / softcap) after the scale
 //   dist        s <- s - r1_h * ln(1 + r2_h * (pos - key)), dist[h] = r1, dist[n_heads + h] = r2
 //   keep_first  with a window: the first keep_first positions stay visible beyond it.  The CTA walks the pages of
 //               the kept positions that lie before its window's first page, then the window's pages
@@ -813,6 +813,16 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
 // significant bits together), so the values' own bfloat16 rounding is the only one of that size in the sum.
 // window >= 0 only (no blocks of positions).
 // ---------------------------------------------------------------------------------------------
+// tanh and ln(1 + x) of the score forms from the hardware's base-2 exponential and logarithm (about 2^-22 of the
+// result's range each: absolute errors near 1e-7, which a capped score of a few tens turns into 1e-5 at most, far below
+// what the bfloat16 queries and keys leave).  Accurate tanhf and log1pf took more instructions per score than the
+// tensor cores' part of the loop.
+__device__ __forceinline__ float tanh_quick(float x) {
+    x = fminf(fmaxf(x, -12.f), 12.f);                      // tanh is 1 to the last bit from 9.1 on
+    return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x));
+}
+__device__ __forceinline__ float log1p_quick(float x) { return __log2f(1.f + x) * 0.69314718056f; }
+
 struct ScoreForms {
     float softcap;             // 0: none
     int keep_first;
@@ -917,8 +927,8 @@ attn_prefill_forms_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const _
                         const int pos = (e & 2) ? p1 : p0;
                         const bool vis = full || (key <= pos && (key >= first_visible_key(pos, window) || key < keep));
                         float v = s[t][e] * scale;
-                        if (f.softcap > 0.f) v = f.softcap * tanhf(v * inv_cap);
-                        if (f.dist != nullptr) v -= r1 * log1pf(r2 * (float)max(pos - key, 0));
+                        if (f.softcap > 0.f) v = f.softcap * tanh_quick(v * inv_cap);
+                        if (f.dist != nullptr) v -= r1 * log1p_quick(r2 * (float)max(pos - key, 0));
                         s[t][e] = vis ? v : -INFINITY;
                     }
                 softmax_update<2, HD / 8>(s, m, l, o);
@@ -1072,8 +1082,8 @@ attn_decode_forms_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __
                     const int half = e >> 1;
                     const bool vis = key < n_keys && (key >= first_key || key < keep);
                     float v = s[t][e] * scale;
-                    if (f.softcap > 0.f) v = f.softcap * tanhf(v * inv_cap);
-                    if (f.dist != nullptr) v -= r1[half] * log1pf(r2[half] * (float)max(pos - key, 0));
+                    if (f.softcap > 0.f) v = f.softcap * tanh_quick(v * inv_cap);
+                    if (f.dist != nullptr) v -= r1[half] * log1p_quick(r2[half] * (float)max(pos - key, 0));
                     s[t][e] = vis ? v : -INFINITY;
                 }
             softmax_update<2, HD / 8>(s, m, l, o);

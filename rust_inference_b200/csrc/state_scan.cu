@@ -55,11 +55,15 @@ struct Prepare {
     const int* cu_seqlens;
     const int* token_seq;
     const int* seq_slot;
+    int tile_ch;               // convolved channels per block: a multiple of unit_dim where there are unit vectors
 };
 
+// A block per (token, tile of p.tile_ch convolved channels); tiles hold whole heads of the unit vectors.  The first
+// tile's block also writes the heads' decays and steps.
 __global__ void __launch_bounds__(256) scan_prepare_kernel(Prepare p) {
-    extern __shared__ float ch[];                 // [conv_ch]
+    extern __shared__ float ch[];                 // [tile_ch]
     const int t = blockIdx.x;
+    const int c0 = blockIdx.y * p.tile_ch, c1 = min(p.conv_ch, c0 + p.tile_ch);
     let_next_kernel_start();
     wait_for_previous_kernels();
     const int b = p.token_seq[t];
@@ -68,7 +72,7 @@ __global__ void __launch_bounds__(256) scan_prepare_kernel(Prepare p) {
     if (!RI_BLOCK_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT)) slot = 0;
     const int K = p.k_taps;
     const float* carried = p.conv_state + (size_t)slot * (K - 1) * p.conv_ch;
-    for (int c = threadIdx.x; c < p.conv_ch; c += blockDim.x) {
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
         float acc = p.conv_bias != nullptr ? p.conv_bias[c] : 0.f;
         for (int k = 0; k < K; ++k) {             // the input k tokens back
             const int src = i - k;
@@ -76,26 +80,30 @@ __global__ void __launch_bounds__(256) scan_prepare_kernel(Prepare p) {
                                      : carried[(size_t)(K - 1 + src) * p.conv_ch + c];
             acc = fmaf(p.taps[(size_t)c * K + (K - 1 - k)], x, acc);
         }
-        ch[c] = silu_f32(acc);
+        ch[c - c0] = silu_f32(acc);
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int h = warp; h < p.unit_heads; h += warps) {
-        float* v = ch + h * p.unit_dim;
-        float ss = 0.f;
-        for (int d = lane; d < p.unit_dim; d += 32) ss = fmaf(v[d], v[d], ss);
-        ss = warp_sum(ss);
-        const float f = (h < p.scaled_heads ? p.unit_scale : 1.f) / sqrtf(ss + 1e-6f);
-        for (int d = lane; d < p.unit_dim; d += 32) v[d] *= f;
+    if (p.unit_heads > 0 && c0 < p.unit_heads * p.unit_dim) {
+        const int h0 = c0 / p.unit_dim, h1 = min(p.unit_heads, c1 / p.unit_dim);     // tiles are multiples of unit_dim there
+        for (int h = h0 + warp; h < h1; h += warps) {
+            float* v = ch + (h - h0) * p.unit_dim;
+            float ss = 0.f;
+            for (int d = lane; d < p.unit_dim; d += 32) ss = fmaf(v[d], v[d], ss);
+            ss = warp_sum(ss);
+            const float f = (h < p.scaled_heads ? p.unit_scale : 1.f) / sqrtf(ss + 1e-6f);
+            for (int d = lane; d < p.unit_dim; d += 32) v[d] *= f;
+        }
+        __syncthreads();
     }
-    __syncthreads();
     float* out = p.out + (size_t)t * p.out_ld;
-    for (int c = threadIdx.x; c < p.conv_ch; c += blockDim.x) out[c] = ch[c];
-    for (int h = threadIdx.x; h < p.heads; h += blockDim.x) {
-        const float dt = softplus_f32(p.z[(size_t)t * p.ld + p.decay_col + h] + p.dt_bias[h]);
-        out[p.conv_ch + h] = expf(-expf(p.a_log[h]) * dt);
-        out[p.conv_ch + p.heads + h] = p.step_col >= 0 ? sigmoid_f32(p.z[(size_t)t * p.ld + p.step_col + h]) : dt;
-    }
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) out[c] = ch[c - c0];
+    if (blockIdx.y == 0)
+        for (int h = threadIdx.x; h < p.heads; h += blockDim.x) {
+            const float dt = softplus_f32(p.z[(size_t)t * p.ld + p.decay_col + h] + p.dt_bias[h]);
+            out[p.conv_ch + h] = expf(-expf(p.a_log[h]) * dt);
+            out[p.conv_ch + p.heads + h] = p.step_col >= 0 ? sigmoid_f32(p.z[(size_t)t * p.ld + p.step_col + h]) : dt;
+        }
 }
 
 __global__ void conv_state_kernel(const float* z, int ld, int conv_col, int conv_ch, int k_taps, float* conv_state,
@@ -303,6 +311,33 @@ __global__ void gated_group_norm_kernel(const float* x, int x_ld, const float* g
     }
 }
 
+// The same with a block per (token, group), for groups of many channels.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm_block_kernel(const float* x, int x_ld, const float* gate, int gate_ld, int gate_col,
+                                        const float* __restrict__ w, int w_len, T* __restrict__ out, int groups,
+                                        int gs, int gate_first, float eps, float out_scale) {
+    __shared__ float scratch[33];
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const int t = blockIdx.x / groups, g = blockIdx.x % groups;
+    const float* src = x + (size_t)t * x_ld + g * gs;
+    const float* gt = gate + (size_t)t * gate_ld + gate_col + g * gs;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+        const float v = gate_first ? src[d] * silu_f32(gt[d]) : src[d];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = out_scale / sqrtf(ss / (float)gs + eps);
+    T* dst = out + ((size_t)t * groups + g) * gs;
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+        const float sg = silu_f32(gt[d]);
+        const float v = gate_first ? src[d] * sg : src[d];
+        const float y = v * inv * w[(g * gs + d) % w_len];
+        dst[d] = from_f32<T>(gate_first ? y : y * sg);
+    }
+}
+
 constexpr int SCAN_SMEM_LIMIT = 44 * 1024;
 
 template <int ROWS>
@@ -328,19 +363,26 @@ RI_API int ri_scan_prepare(const float* z, int ld, int conv_col, int conv_ch, co
                            int out_ld, const int* cu_seqlens, const int* token_seq, const int* seq_slot, int n_tokens,
                            int n_seqs, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (k_taps < 1) return fail("scan_prepare: a convolution of %d taps", k_taps);
+    if (k_taps < 1 || conv_ch < 1) return fail("scan_prepare: a convolution of %d taps over %d channels", k_taps, conv_ch);
     if (conv_col < 0 || conv_col + conv_ch > ld || decay_col + heads > ld || step_col + heads > ld)
         return fail("scan_prepare: columns beyond the projection's %d", ld);
     if (unit_heads * unit_dim > conv_ch || scaled_heads > unit_heads) return fail("scan_prepare: unit vectors beyond the convolved channels");
     if (out_ld < conv_ch + 2 * heads) return fail("scan_prepare: output rows of %d values are too short", out_ld);
-    const size_t smem = (size_t)conv_ch * sizeof(float);
-    if (smem > 200 * 1024) return fail("scan_prepare: %d convolved channels do not fit shared memory", conv_ch);
+    // tiles of about 512 channels; where heads are made unit vectors a tile holds whole heads (a head wider than that
+    // is a tile of its own)
+    int tile_ch = 512;
+    if (unit_heads > 0 && unit_dim > 0) tile_ch = unit_dim * ((512 + unit_dim - 1) / unit_dim);
+    if (tile_ch > conv_ch) tile_ch = conv_ch;
+    const size_t smem = (size_t)tile_ch * sizeof(float);
+    if (smem > 200 * 1024) return fail("scan_prepare: heads of %d channels do not fit shared memory", unit_dim);
     static PerDeviceOnce once;
     if (smem > 48 * 1024)
         if (int rc = raise_dynamic_smem(scan_prepare_kernel, 200 * 1024, once, "scan_prepare")) return rc;
+    const int tiles = (conv_ch + tile_ch - 1) / tile_ch;
+    if (tiles > 65535) return fail("scan_prepare: %d tiles of channels exceed the grid limit", tiles);
     Prepare p{z, ld, conv_col, conv_ch, taps, conv_bias, k_taps, conv_state, unit_heads, unit_dim, scaled_heads, unit_scale,
-              heads, decay_col, step_col, a_log, dt_bias, out, out_ld, cu_seqlens, token_seq, seq_slot};
-    cudaError_t e = launch_dependent(scan_prepare_kernel, n_tokens, 256, smem, stream, p);
+              heads, decay_col, step_col, a_log, dt_bias, out, out_ld, cu_seqlens, token_seq, seq_slot, tile_ch};
+    cudaError_t e = launch_dependent(scan_prepare_kernel, dim3(n_tokens, tiles), 256, smem, stream, p);
     if (check_launch(e, "scan_prepare")) return 1;
     if (k_taps > 1) {
         dim3 grid((conv_ch + 127) / 128, n_seqs);
@@ -379,13 +421,18 @@ RI_API int ri_gated_group_norm(const float* x, int x_ld, const float* gate, int 
     if (groups <= 0 || gs <= 0 || w_len <= 0) return fail("gated_group_norm: %d groups of %d channels, %d weights", groups, gs, w_len);
     const long long warps = (long long)n_tokens * groups;
     const int blocks = (int)((warps * 32 + 255) / 256);
+    const bool wide = gs >= 512 && warps <= 0x7fffffffLL;          // a block per group instead of a warp
     cudaError_t e;
     if (dtype == RI_F32)
-        e = launch_dependent(gated_group_norm_kernel<float>, blocks, 256, 0, stream, x, x_ld, gate, gate_ld, gate_col, w, w_len,
-                             (float*)out, n_tokens, groups, gs, gate_first, eps, out_scale);
+        e = wide ? launch_dependent(gated_group_norm_block_kernel<float>, (int)warps, 256, 0, stream, x, x_ld, gate, gate_ld, gate_col,
+                                    w, w_len, (float*)out, groups, gs, gate_first, eps, out_scale)
+                 : launch_dependent(gated_group_norm_kernel<float>, blocks, 256, 0, stream, x, x_ld, gate, gate_ld, gate_col, w, w_len,
+                                    (float*)out, n_tokens, groups, gs, gate_first, eps, out_scale);
     else if (dtype == RI_BF16)
-        e = launch_dependent(gated_group_norm_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, x_ld, gate, gate_ld, gate_col, w, w_len,
-                             (__nv_bfloat16*)out, n_tokens, groups, gs, gate_first, eps, out_scale);
+        e = wide ? launch_dependent(gated_group_norm_block_kernel<__nv_bfloat16>, (int)warps, 256, 0, stream, x, x_ld, gate, gate_ld,
+                                    gate_col, w, w_len, (__nv_bfloat16*)out, groups, gs, gate_first, eps, out_scale)
+                 : launch_dependent(gated_group_norm_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, x_ld, gate, gate_ld, gate_col, w,
+                                    w_len, (__nv_bfloat16*)out, n_tokens, groups, gs, gate_first, eps, out_scale);
     else
         return fail("gated_group_norm: unknown dtype %d", dtype);
     return check_launch(e, "gated_group_norm");

@@ -185,8 +185,7 @@ class GQAttention(Mixer):
 
     def forward(self, x, residual, ctx, cache_layer, writes_cache):
         n = x.shape[0]
-        if not writes_cache and self.own_kv:
-            raise ValueError("a layer with key and value projections writes its own cache")
+        # a layer that has key and value projections but is scheduled to read another layer's cache leaves its own unused
         kv_width = (self.kv_dim + (0 if self.values_from_keys else self.v_dim)) if self.own_kv else 0
         gate_col = self.q_dim + kv_width
         width = self.w_qkv.n                           # with gates: one more column per head, padded to a multiple of 8

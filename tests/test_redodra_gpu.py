@@ -163,7 +163,8 @@ def test_activation_in_the_product_s_epilogue(dtype, n, width, ff):
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("groups,size,w_len,gate_first", [(4, 24, 24, False), (1, 72, 72, False), (2, 64, 128, True),
-                                                         (3, 40, 120, True), (8, 8, 8, False), (1, 130, 130, True)])
+                                                         (3, 40, 120, True), (8, 8, 8, False), (1, 130, 130, True), (2, 640, 640, True),
+                                                         (1, 1030, 1030, False)])
 def test_gated_group_norm_kernel(out_dtype, groups, size, w_len, gate_first):
     """RMS norm over groups of channels with a silu gate before or after it; one weight for all groups or one per channel."""
     from rust_inference_b200.kernels import ops
