@@ -78,7 +78,7 @@ template <int MODE>
 __device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2, const GateForm& gf,
                                              const ActForm& af) {
     if (MODE == 4) {
-        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(act_f32(acc, af));
+        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(act_quick_f32(acc, af));
     } else if (MODE == 0) {
         reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + bias);
     } else if (MODE == 1) {
@@ -377,7 +377,7 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
         for (int j = 0; j < 16; ++j) {
             const float a = __uint_as_float(v[j]);
             if (MODE == 3) r[j] = gated_to_bf16(a, __uint_as_float(u[j]), gf);
-            else if (MODE == 4) r[j] = act_f32(a, af);
+            else if (MODE == 4) r[j] = act_quick_f32(a, af);
             else if (MODE == 2) r[j] = a;
             else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
         }
