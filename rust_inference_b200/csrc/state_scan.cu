@@ -156,14 +156,26 @@ struct Scan {
     const int* seq_slot;
     int heads, groups, dim, vdim, tile_t;
     int vec;                   // 1: rows, columns and sizes allow 16-byte copies
+    int piece, max_pieces;     // passes over pieces: tokens per piece, most pieces of a sequence
+    float* piece_state;        // [seqs, max_pieces, heads, dim, vdim]: a piece's end state from zero, then its start state
+    float* piece_decay;        // [seqs, max_pieces, heads]: the product of a piece's decays
 };
 
-template <int ROWS, bool DELTA>
+// How a launch of the scan treats its tokens.  WHOLE: a block runs over all new tokens of its sequence from the slot's
+// state and writes the state back.  For long runs of the state space, whose update is linear in the state with a scalar
+// factor, three launches work on pieces of a sequence side by side: LOCAL scans every piece from zero (no read-out) and
+// keeps its end state and the product of its decays; a carry kernel walks the pieces of a sequence per state element,
+// start(p + 1) = decays(p) * start(p) + end(p), leaving every piece's start state and the sequence's final state in the
+// slot; FINAL scans every piece again from its start state and writes the read-outs.
+enum { WHOLE = 0, LOCAL = 1, FINAL = 2 };
+
+template <int ROWS, bool DELTA, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
     constexpr int SLICE = ROWS + 4;
     constexpr int TOKEN = 2 * R * SLICE + COLS + 4;       // k, q, the block's values, decay and step
     extern __shared__ __align__(16) float tile[];          // two tiles of tile_t tokens
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
+    const int b = MODE == WHOLE ? blockIdx.x : blockIdx.x / p.max_pieces, h = blockIdx.y, j0 = blockIdx.z * COLS;
+    const int pc = MODE == WHOLE ? 0 : blockIdx.x % p.max_pieces;
     const int r = threadIdx.x % R, jj = threadIdx.x / R;
     const int j = j0 + jj, i0 = r * ROWS;
     const bool live = j < p.vdim;
@@ -171,13 +183,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
     const float skip = p.skip != nullptr ? p.skip[h] : 0.f;
     let_next_kernel_start();
     wait_for_previous_kernels();
-    const int t0 = p.cu_seqlens[b], t1 = p.cu_seqlens[b + 1];
+    const int t0 = p.cu_seqlens[b] + (MODE == WHOLE ? 0 : pc * p.piece);
+    const int t1 = MODE == WHOLE ? p.cu_seqlens[b + 1] : min(p.cu_seqlens[b + 1], t0 + p.piece);
     const int slot = p.seq_slot[b];
     if (t0 >= t1 || !RI_BLOCK_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT)) return;
-    float* S = p.state + (((size_t)slot * p.heads + h) * p.dim) * p.vdim;
+    float* S = MODE == WHOLE ? p.state + (((size_t)slot * p.heads + h) * p.dim) * p.vdim
+                             : p.piece_state + ((((size_t)b * p.max_pieces + pc) * p.heads + h) * p.dim) * p.vdim;
     float s[ROWS];
 #pragma unroll
-    for (int k = 0; k < ROWS; ++k) s[k] = (live && i0 + k < p.dim) ? S[(size_t)(i0 + k) * p.vdim + j] : 0.f;
+    for (int k = 0; k < ROWS; ++k) s[k] = (MODE != LOCAL && live && i0 + k < p.dim) ? S[(size_t)(i0 + k) * p.vdim + j] : 0.f;
+    float decays = 1.f;
     const int g = h / (p.heads / p.groups);
     const int q_off = p.q_col + g * p.dim, k_off = p.k_col + g * p.dim, v_off = p.v_col + h * p.vdim + j0;
     const int cols = min(COLS, p.vdim - j0);
@@ -248,6 +263,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
                 qq[4 * k] = qv.x; qq[4 * k + 1] = qv.y; qq[4 * k + 2] = qv.z; qq[4 * k + 3] = qv.w;
             }
             float write = step * v;
+            if (MODE == LOCAL) decays *= a;
             if (DELTA) {
                 float d0 = 0.f, d1 = 0.f;
 #pragma unroll
@@ -273,13 +289,39 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(Scan p) {
             float acc = a0 + a1;
 #pragma unroll
             for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && r == 0) p.o[(size_t)(tb + tok) * o_ld + h * p.vdim + j] = fmaf(skip, v, acc);
+            if (MODE != LOCAL && live && r == 0) p.o[(size_t)(tb + tok) * o_ld + h * p.vdim + j] = fmaf(skip, v, acc);
         }
         __syncthreads();                                  // this tile may be overwritten by the fetch after next
     }
+    if (MODE == FINAL) return;                            // the carry kernel left the final state in the slot
 #pragma unroll
     for (int k = 0; k < ROWS; ++k)
         if (live && i0 + k < p.dim) S[(size_t)(i0 + k) * p.vdim + j] = s[k];
+    if (MODE == LOCAL && blockIdx.z == 0 && threadIdx.x == 0) p.piece_decay[((size_t)b * p.max_pieces + pc) * p.heads + h] = decays;
+}
+
+// Per (sequence, head, state element): the pieces' start states from their end states and decay products; the
+// sequence's final state goes to the slot.
+__global__ void __launch_bounds__(256) scan_carry_kernel(float* state, float* piece_state, const float* piece_decay,
+                                                         const int* cu_seqlens, const int* seq_slot, int heads, int per_head,
+                                                         int piece, int max_pieces) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+    const int slot = seq_slot[b];
+    if (e >= per_head || n <= 0 || !RI_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT)) return;
+    const int pieces = (n + piece - 1) / piece;
+    float* dst = state + ((size_t)slot * heads + h) * per_head + e;
+    float s = *dst;
+    for (int pc = 0; pc < pieces; ++pc) {
+        float* ps = piece_state + (((size_t)b * max_pieces + pc) * heads + h) * per_head + e;
+        const float local = *ps;
+        *ps = s;
+        s = fmaf(piece_decay[((size_t)b * max_pieces + pc) * heads + h], s, local);
+    }
+    *dst = s;
 }
 
 // One warp per (token, group of `gs` channels): with gate_first the channels are multiplied by silu(gate) and then
@@ -341,7 +383,7 @@ __global__ void __launch_bounds__(256) gated_group_norm_block_kernel(const float
 constexpr int SCAN_SMEM_LIMIT = 44 * 1024;
 
 template <int ROWS>
-int launch_scan(bool delta, dim3 grid, cudaStream_t stream, Scan p, int longest) {
+int launch_scan(bool delta, dim3 grid, cudaStream_t stream, Scan p, int longest, int n_seqs) {
     const int token_bytes = (2 * R * (ROWS + 4) + COLS + 4) * (int)sizeof(float);
     int tile_t = SCAN_SMEM_LIMIT / (2 * token_bytes);     // two tiles
     if (tile_t > 16) tile_t = 16;
@@ -350,8 +392,20 @@ int launch_scan(bool delta, dim3 grid, cudaStream_t stream, Scan p, int longest)
     p.tile_t = tile_t;
     const size_t smem = (size_t)2 * tile_t * token_bytes;
     cudaError_t e;
-    if (delta) e = launch_dependent(state_scan_kernel<ROWS, true>, grid, SCAN_THREADS, smem, stream, p);
-    else e = launch_dependent(state_scan_kernel<ROWS, false>, grid, SCAN_THREADS, smem, stream, p);
+    if (delta) {
+        e = launch_dependent(state_scan_kernel<ROWS, true, WHOLE>, grid, SCAN_THREADS, smem, stream, p);
+    } else if (p.piece <= 0) {
+        e = launch_dependent(state_scan_kernel<ROWS, false, WHOLE>, grid, SCAN_THREADS, smem, stream, p);
+    } else {
+        const dim3 pieces(grid.x * p.max_pieces, grid.y, grid.z);
+        e = launch_dependent(state_scan_kernel<ROWS, false, LOCAL>, pieces, SCAN_THREADS, smem, stream, p);
+        if (check_launch(e, "state_scan (pieces from zero)")) return 1;
+        const int per_head = p.dim * p.vdim;
+        e = launch_dependent(scan_carry_kernel, dim3((per_head + 255) / 256, p.heads, n_seqs), 256, 0, stream, p.state, p.piece_state,
+                             (const float*)p.piece_decay, p.cu_seqlens, p.seq_slot, p.heads, per_head, p.piece, p.max_pieces);
+        if (check_launch(e, "state_scan (carry)")) return 1;
+        e = launch_dependent(state_scan_kernel<ROWS, false, FINAL>, pieces, SCAN_THREADS, smem, stream, p);
+    }
     return check_launch(e, "state_scan");
 }
 
@@ -395,10 +449,13 @@ RI_API int ri_scan_prepare(const float* z, int ld, int conv_col, int conv_ch, co
 // u: float32 [n_tokens, ld] with the columns of queries and keys ([groups, dim] each), values ([heads, vdim]), decays and
 // steps ([heads] each).  state: float32 [slots, heads, dim, vdim].  o: float32 [n_tokens, heads * vdim].
 // delta != 0: the gated delta rule; else the state space (with skip [heads] or null).  longest_run: the most new tokens
-// any sequence brings (0: unknown), which sizes the scan's shared memory.
+// any sequence brings (0: unknown), which sizes the scan's shared memory.  piece > 0 (state space only): the three passes
+// over pieces of that many tokens, with scratch piece_state [n_seqs, max_pieces, heads, dim, vdim] and piece_decay
+// [n_seqs, max_pieces, heads]; max_pieces * piece covers the longest run.
 RI_API int ri_state_scan(const float* u, int ld, int q_col, int k_col, int v_col, int decay_col, int step_col, const float* skip,
                          float* state, float* o, const int* cu_seqlens, const int* seq_slot, int n_seqs, int heads, int groups,
-                         int dim, int vdim, int delta, int longest_run, cudaStream_t stream) {
+                         int dim, int vdim, int delta, int longest_run, int piece, int max_pieces, float* piece_state,
+                         float* piece_decay, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (groups <= 0 || heads % groups) return fail("state_scan: %d heads are not a multiple of %d groups", heads, groups);
     if (heads > 65535) return fail("state_scan: %d heads exceed the grid limit", heads);
@@ -406,12 +463,19 @@ RI_API int ri_state_scan(const float* u, int ld, int q_col, int k_col, int v_col
     int rows = (dim + R - 1) / R;
     rows = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
     const int vec = ((ld | q_col | k_col | v_col | dim | vdim) % 4 == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0) ? 1 : 0;
-    Scan p{u, ld, q_col, k_col, v_col, decay_col, step_col, skip, state, o, cu_seqlens, seq_slot, heads, groups, dim, vdim, 1, vec};
+    if (piece > 0) {
+        if (delta) return fail("state_scan: the delta rule's update is not a scalar times the state: no pieces");
+        if (max_pieces < 1 || piece_state == nullptr || piece_decay == nullptr) return fail("state_scan: pieces need their scratch");
+        if ((long long)n_seqs * max_pieces > 0x7fffffffLL || n_seqs > 65535) return fail("state_scan: %d sequences of %d pieces exceed the grid limit", n_seqs, max_pieces);
+        if (longest_run <= 0 || longest_run > piece) longest_run = piece;
+    }
+    Scan p{u, ld, q_col, k_col, v_col, decay_col, step_col, skip, state, o, cu_seqlens, seq_slot, heads, groups, dim, vdim, 1, vec,
+           piece > 0 ? piece : 0, piece > 0 ? max_pieces : 1, piece_state, piece_decay};
     dim3 grid(n_seqs, heads, (vdim + COLS - 1) / COLS);
-    if (rows == 4) return launch_scan<4>(delta != 0, grid, stream, p, longest_run);
-    if (rows == 8) return launch_scan<8>(delta != 0, grid, stream, p, longest_run);
-    if (rows == 16) return launch_scan<16>(delta != 0, grid, stream, p, longest_run);
-    return launch_scan<32>(delta != 0, grid, stream, p, longest_run);
+    if (rows == 4) return launch_scan<4>(delta != 0, grid, stream, p, longest_run, n_seqs);
+    if (rows == 8) return launch_scan<8>(delta != 0, grid, stream, p, longest_run, n_seqs);
+    if (rows == 16) return launch_scan<16>(delta != 0, grid, stream, p, longest_run, n_seqs);
+    return launch_scan<32>(delta != 0, grid, stream, p, longest_run, n_seqs);
 }
 
 RI_API int ri_gated_group_norm(const float* x, int x_ld, const float* gate, int gate_ld, int gate_col, const float* w, int w_len,

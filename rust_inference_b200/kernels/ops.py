@@ -985,12 +985,21 @@ def scan_prepare(z: torch.Tensor, *, conv_col: int, conv_ch: int, taps: torch.Te
 
 def state_scan(u: torch.Tensor, state: torch.Tensor, o: torch.Tensor, cu_seqlens, seq_slot, *, n_seqs: int, heads: int,
                groups: int, dim: int, vdim: int, q_col: int, k_col: int, v_col: int, decay_col: int, step_col: int,
-               delta: bool, skip=None, longest_run: int = 0) -> torch.Tensor:
+               delta: bool, skip=None, longest_run: int = 0, piece: int = 0, max_pieces: int = 1, piece_state=None,
+               piece_decay=None) -> torch.Tensor:
     """The recurrence over every sequence's new tokens from its slot's state (float32 [slots, heads, dim, vdim]), which
     moves on.  u: float32 [T, ld] with the columns of queries and keys ([groups, dim] each), values ([heads, vdim]),
     decays and steps ([heads] each); o: float32 [T, heads * vdim].  delta: the gated delta rule
-    (S <- a S; S += k (step (v - S^T k))^T); else S <- a S + k (step v)^T and o += skip * v."""
-    _need_cuda(u, state, o, cu_seqlens, seq_slot, skip)
+    (S <- a S; S += k (step (v - S^T k))^T); else S <- a S + k (step v)^T and o += skip * v.  piece > 0 (not the delta
+    rule): long runs are scanned in pieces of that many tokens side by side, from zero, then again from start states that
+    a carry over the pieces gives; float32 scratch piece_state [n_seqs, max_pieces, heads, dim, vdim] and piece_decay
+    [n_seqs, max_pieces, heads], max_pieces * piece at least the longest run."""
+    _need_cuda(u, state, o, cu_seqlens, seq_slot, skip, piece_state, piece_decay)
+    if piece > 0:
+        _need(not delta and piece_state is not None and piece_decay is not None and piece_state.dtype == torch.float32
+              and piece_decay.dtype == torch.float32 and piece_state.is_contiguous() and piece_decay.is_contiguous()
+              and piece_state.numel() >= n_seqs * max_pieces * heads * dim * vdim
+              and piece_decay.numel() >= n_seqs * max_pieces * heads, "state_scan: scratch of the pieces")
     _need(u.dtype == torch.float32 and u.is_contiguous() and o.dtype == torch.float32 and o.is_contiguous()
           and tuple(o.shape) == (u.shape[0], heads * vdim), "state_scan: u and o must be float32")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
@@ -999,8 +1008,22 @@ def state_scan(u: torch.Tensor, state: torch.Tensor, o: torch.Tensor, cu_seqlens
         _f32_vec(skip, heads, "state_scan: skip")
     _call("state_scan", "ri_state_scan", _p(u), c_int(u.shape[1]), c_int(q_col), c_int(k_col), c_int(v_col), c_int(decay_col),
           c_int(step_col), _p(skip), _p(state), _p(o), _p(cu_seqlens), _p(seq_slot), c_int(n_seqs), c_int(heads), c_int(groups),
-          c_int(dim), c_int(vdim), c_int(1 if delta else 0), c_int(longest_run), _stream())
+          c_int(dim), c_int(vdim), c_int(1 if delta else 0), c_int(longest_run), c_int(piece), c_int(max_pieces),
+          _p(piece_state), _p(piece_decay), _stream())
     return o
+
+
+SCAN_PIECE = 64                 # tokens of a long run of new tokens that one block of the state space's scan takes
+
+
+def scan_pieces(max_new: int, blocks: int) -> tuple:
+    """(piece, most pieces per sequence) of the state space's scan for a step whose longest run of new tokens is
+    max_new and whose one-pass grid has `blocks` blocks (sequences x heads x tiles of 16 value columns): (0, 1), one
+    pass per sequence, for runs of up to two pieces and for grids that fill the SMs by themselves (the passes over
+    pieces do the multiply-adds twice: measured, they halve the time at 64 blocks, change nothing at 128 and lose at 256)."""
+    if max_new <= 2 * SCAN_PIECE or blocks > torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count:
+        return 0, 1
+    return SCAN_PIECE, -(-max_new // SCAN_PIECE)
 
 
 def gated_group_norm(x: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, out: torch.Tensor, *,

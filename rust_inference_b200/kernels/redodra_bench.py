@@ -121,6 +121,11 @@ def time_parts(engine, s: dict, lens_before: list, new_tokens: int, peaks: dict,
                                             seq_slot=ctx.seq_slot, n_seqs=ctx.n_seqs, **prepare_kw))
         row(tag + "_prepare", ms, 0.0, n * (part.conv_ch * 8 + 4 * H * 4) + 2 * B * carried.state[0].numel() * 4)
         o = torch.empty(n, H * vdim, dtype=f32, device=dev)
+        piece, max_pieces = (0, 1) if delta else ops.scan_pieces(ctx.max_new, ctx.n_seqs * H * -(-vdim // 16))     # as the part calls it
+        if piece:
+            scan_kw = dict(scan_kw, piece=piece, max_pieces=max_pieces,
+                           piece_state=torch.empty(ctx.n_seqs, max_pieces, H, dim, vdim, dtype=f32, device=dev),
+                           piece_decay=torch.empty(ctx.n_seqs, max_pieces, H, dtype=f32, device=dev))
         ms = timer(lambda: ops.state_scan(u, matrix.state, o, ctx.cu_seqlens, ctx.seq_slot, n_seqs=ctx.n_seqs, heads=H, groups=groups,
                                           dim=dim, vdim=vdim, delta=delta, longest_run=ctx.max_new, **scan_kw))
         # the prepared rows read (keys and queries once per head that shares them), the result written, every state read

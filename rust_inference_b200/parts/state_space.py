@@ -96,10 +96,16 @@ class SelectiveStateSpace(Mixer):
                          decay_col=2 * self.inner + 2 * gn, step_col=-1, a_log=self.a_log, dt_bias=self.dt_bias, out=u,
                          cu_seqlens=ctx.cu_seqlens, token_seq=ctx.token_seq, seq_slot=ctx.seq_slot, n_seqs=ctx.n_seqs)
         y = ctx.buffer("scan_o", (n, self.inner), torch.float32)
+        piece, max_pieces = ops.scan_pieces(ctx.max_new, ctx.n_seqs * H * -(-self.v_head_dim // 16))
+        pieces = {}
+        if piece:                      # a long run of new tokens: its pieces side by side, from zero and again from their start states
+            pieces = {"piece": piece, "max_pieces": max_pieces,
+                      "piece_state": ctx.buffer("scan_piece_state", (ctx.n_seqs, max_pieces, H, self.state, self.v_head_dim), torch.float32),
+                      "piece_decay": ctx.buffer("scan_piece_decay", (ctx.n_seqs, max_pieces, H), torch.float32)}
         ops.state_scan(u, matrix.state, y, ctx.cu_seqlens, ctx.seq_slot, n_seqs=ctx.n_seqs, heads=H, groups=self.groups,
                        dim=self.state, vdim=self.v_head_dim, q_col=self.inner + gn, k_col=self.inner, v_col=0,
                        decay_col=self.conv_ch, step_col=self.conv_ch + H, delta=False, skip=self.skip,
-                       longest_run=ctx.max_new)
+                       longest_run=ctx.max_new, **pieces)
         normed = ctx.buffer("scan_normed", (n, self.inner), self.dtype)
         ops.gated_group_norm(y, z, 0, self.norm, normed, groups=self.norm_groups, group_size=self.inner // self.norm_groups,
                              gate_first=True, eps=self.eps, out_scale=self.out_scale)
