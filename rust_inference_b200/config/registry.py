@@ -18,15 +18,19 @@ class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], Any]   # config.json dict -> typed config
     build_spec: Callable[[Any], Any]                    # typed config -> parts.spec.ModelSpec
+    # True: parse_config also takes `shapes` (tensor name -> shape of the folder's weight file), for a size that
+    # config.json leaves to a tensor's shape
+    reads_shapes: bool = False
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, build_spec, *, replace: bool = False) -> Architecture:
+def register_architecture(name: str, parse_config, build_spec, *, replace: bool = False,
+                          reads_shapes: bool = False) -> Architecture:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    arch = Architecture(name, parse_config, build_spec)
+    arch = Architecture(name, parse_config, build_spec, reads_shapes)
     _ARCHITECTURES[name] = arch
     return arch
 
@@ -65,8 +69,28 @@ def config_from_dict(d: Mapping[str, Any]):
     return get_architecture(architecture_name(d)).parse_config(d)
 
 
+def _folder_shapes(model_dir: str) -> dict:
+    """Tensor name -> shape from the folder's weight file (its header only); empty without one."""
+    from ..weights.safetensors_io import ModelFiles
+    try:
+        files = ModelFiles(model_dir)
+    except (OSError, ValueError):
+        return {}
+    try:
+        return {name: tuple(files.shape(name)) for name in files.names()}
+    finally:
+        files.close()
+
+
+def _parse(arch: Architecture, d: Mapping[str, Any], model_dir: str):
+    if arch.reads_shapes:
+        return arch.parse_config(d, shapes=_folder_shapes(model_dir))
+    return arch.parse_config(d)
+
+
 def load_config(model_dir: str):
-    return config_from_dict(read_config_json(model_dir))
+    d = read_config_json(model_dir)
+    return _parse(get_architecture(architecture_name(d)), d, model_dir)
 
 
 def load_spec(model_dir: str):
@@ -74,10 +98,10 @@ def load_spec(model_dir: str):
     architecture, which parses the config and builds the spec."""
     d = read_config_json(model_dir)
     arch = get_architecture(architecture_name(d))
-    config = arch.parse_config(d)
+    config = _parse(arch, d, model_dir)
     return config, arch.build_spec(config)
 
 
 def _ensure_builtin() -> None:
     # The built-in models register themselves on import.
-    from ..models import dense_decoder, lulisun, vadodra, redodra  # noqa: F401
+    from ..models import dense_decoder, lulisun, vadodra, redodra, belizen  # noqa: F401

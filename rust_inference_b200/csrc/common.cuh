@@ -101,15 +101,19 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int span) {
 }
 
 // The form of a gated feed-forward's activation, for the contractions' gated epilogue:
-//   act(g, u) = g' * sigmoid(alpha * g') * (u' + shift),   g' = min(g, limit),  u' = clamp(u, -limit, limit).
-// Three floats in device memory {alpha, limit, shift}; a null pointer stands for SiLU(g) * u (alpha 1, no limit,
-// shift 0), which the formulas below reproduce exactly with those values.
-struct GateForm { float alpha, limit, shift; };
+//   act(g, u) = mult * g' * sigmoid(alpha * g' * (1 + cubic * g'^2)) * (u' + shift),
+//   g' = min(g, limit),  u' = clamp(u, -limit, limit).
+// Five floats in device memory {alpha, limit, shift, cubic, mult}; a null pointer stands for SiLU(g) * u (alpha 1, no
+// limit, shift 0, cubic 0, mult 1), which the formulas below reproduce exactly with those values.  With alpha =
+// 2 sqrt(2 / pi) and cubic = 0.044715 the gate is the tanh form of GELU: 0.5 z (1 + tanh(y)) = z sigmoid(2 y).
+struct GateForm { float alpha, limit, shift, cubic, mult; };
 __device__ __forceinline__ GateForm load_gate_form(const float* p) {
     GateForm f;
     f.alpha = p != nullptr ? p[0] : 1.f;
     f.limit = p != nullptr ? p[1] : INFINITY;
     f.shift = p != nullptr ? p[2] : 0.f;
+    f.cubic = p != nullptr ? p[3] : 0.f;
+    f.mult = p != nullptr ? p[4] : 1.f;
     return f;
 }
 
@@ -152,10 +156,10 @@ __device__ __forceinline__ float silu_f32(float x) {
 __device__ __forceinline__ float gated_f32(float g, float u, const GateForm& f) {
     g = fminf(g, f.limit);
     u = fmaxf(fminf(u, f.limit), -f.limit) + f.shift;
-    if (f.alpha == 1.f) return silu_f32(g) * u;
-    const float z = f.alpha * g;
+    if (f.alpha == 1.f && f.cubic == 0.f) return silu_f32(g) * u * f.mult;
+    const float z = f.alpha * g * fmaf(f.cubic * g, g, 1.f);
     const float sig = z >= 0.f ? 1.f / (1.f + expf(-z)) : expf(z) / (1.f + expf(z));
-    return g * sig * u;
+    return g * sig * u * f.mult;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -1170,6 +1170,79 @@ RI_API int ri_scale(void* x, int dtype, long long n, float factor, cudaStream_t 
     return check_launch(e, "scale");
 }
 
+namespace {
+// x[t, d] += other[t, d] + row[d]; either may be absent.
+__global__ void stream_add_kernel(float* x, const float* other, const float* __restrict__ row, size_t total, int width) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (other != nullptr) v += other[i];
+        if (row != nullptr) v += row[i % width];
+        x[i] = v;
+    }
+}
+
+// x[t, c] *= sigmoid(gate[t, gate_col + c]) * factor, the product formed in float32 and rounded once.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* x, const T* gate, int gate_ld, int gate_col, size_t total, int width, float factor) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width;
+        const int c = (int)(i % width);
+        const float g = to_f32<T>(gate[t * gate_ld + gate_col + c]);
+        const float sig = g >= 0.f ? 1.f / (1.f + expf(-g)) : expf(g) / (1.f + expf(g));
+        x[i] = from_f32<T>(to_f32<T>(x[i]) * sig * factor);
+    }
+}
+
+// x = cap * tanh(x / cap)
+__global__ void softcap_kernel(float* x, size_t total, float cap) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const float inv = 1.f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+}  // namespace
+
+// x (float32 [n_rows, width]) += other (the same shape, or null) + row (float32 [width], or null), in place.
+RI_API int ri_stream_add(float* x, const float* other, const float* row, int n_rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * width;
+    if (total == 0 || (other == nullptr && row == nullptr)) return 0;
+    const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    cudaError_t e = launch_dependent(stream_add_kernel, blocks, 256, 0, stream, x, other, row, total, width);
+    return check_launch(e, "stream_add");
+}
+
+// x ([n_rows, width], contiguous) *= sigmoid(gate[:, gate_col .. gate_col + width]) * factor; gate has rows of gate_ld values.
+RI_API int ri_sigmoid_gate(void* x, const void* gate, int dtype, int gate_ld, int gate_col, int n_rows, int width, float factor,
+                           cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * width;
+    if (total == 0) return 0;
+    if (gate_col < 0 || gate_ld < gate_col + width) return fail("sigmoid_gate: rows of %d values hold no %d gates from column %d", gate_ld, width, gate_col);
+    const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    cudaError_t e;
+    if (dtype == RI_F32)
+        e = launch_dependent(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (float*)x, (const float*)gate, gate_ld, gate_col,
+                             total, width, factor);
+    else if (dtype == RI_BF16)
+        e = launch_dependent(sigmoid_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)x,
+                             (const __nv_bfloat16*)gate, gate_ld, gate_col, total, width, factor);
+    else return fail("sigmoid_gate: unknown dtype %d", dtype);
+    return check_launch(e, "sigmoid_gate");
+}
+
+// x (float32, n values) = cap * tanh(x / cap), in place.
+RI_API int ri_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return fail("softcap: a cap of %f is not positive", (double)cap);
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    cudaError_t e = launch_dependent(softcap_kernel, blocks, 256, 0, stream, x, (size_t)n, cap);
+    return check_launch(e, "softcap");
+}
+
 RI_API int ri_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;

@@ -71,7 +71,7 @@ __device__ __forceinline__ float silu_to_bf16(float x) { return __fdividef(x, 1.
 __device__ __forceinline__ float gated_to_bf16(float g, float u, const GateForm& f) {
     g = fminf(g, f.limit);
     u = fmaxf(fminf(u, f.limit), -f.limit) + f.shift;
-    return __fdividef(g, 1.f + __expf(-f.alpha * g)) * u;
+    return __fdividef(g, 1.f + __expf(-f.alpha * g * fmaf(f.cubic * g, g, 1.f))) * u * f.mult;
 }
 
 template <int MODE>

@@ -7,11 +7,15 @@
 //             ranking, whatever the sign of their c); the `top` candidates with the highest c are
 //             taken, with weights s / (sum of the taken s + 1e-20).
 //             Optionally one more number per token: sigmoid(w_gate . h), the gate of a shared expert.
+//             Another form (`form` bit 0): s = softmax(W_router h) over all experts instead of the sigmoid; and
+//             (bit 1) the weights are the taken s as they are, not divided by their sum.
 //   arrange   the (token, choice) pairs listed expert by expert, cut into tiles of rows that belong
 //             to one expert
 //   experts   the grouped contractions on the FFMA pipe with float32 accumulation, any sizes:
 //             act[p] = silu(Wg[e] h) * (Wu[e] h) and y[p] = Wd[e] act[p] for pair p of expert e
-//   combine   residual[t] += sum_c weight[t, c] * y[t * top + c] (+ gate[t] * shared[t]), in a fixed order
+//   combine   residual[t] += scale * (sum_c weight[t, c] * y[t * top + c] (+ gate[t] * shared[t])), in a fixed order;
+//             a chosen id at or beyond the number of experts with tensors is an expert that hands its input
+//             through: its y is the token's input row itself
 //
 // Every kernel here runs behind others of the same step and may come onto the SMs before they have
 // finished (programmatic dependent launch): what an earlier kernel of the step wrote is read after
@@ -69,7 +73,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* x, const float* __restrict__ router, const float* __restrict__ correction,
                  const float* __restrict__ gate_w, int* __restrict__ ids, float* __restrict__ weights,
                  float* __restrict__ gate_out, int n_tokens, int width, int experts, int top, int groups, int keep,
-                 int per_block) {
+                 int per_block, int form) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stride = 2 * experts + groups;
@@ -110,7 +114,7 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
             if (lane == 0) {
                 const float s = sigmoid_f32(a);
                 if (e < experts) {
-                    smem[k * stride + e] = s;
+                    smem[k * stride + e] = (form & 1) ? a : s;           // softmax: the logit, turned into a score below
                     smem[k * stride + experts + e] = s + correction[e];
                 } else {
                     gate_out[tok0 + k] = s;
@@ -124,6 +128,21 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
     float* score = smem + (size_t)warp * stride;
     float* choice = score + experts;
     float* gscore = choice + experts;
+    if (form & 1) {
+        // softmax over all experts, in float32: the maximum, the exponentials' sum, the scores
+        float mx = -INFINITY;
+        for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, score[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < experts; e += 32) sum += expf(score[e] - mx);
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) {
+            const float s = expf(score[e] - mx) / sum;
+            score[e] = s;
+            choice[e] = s + correction[e];
+        }
+        __syncwarp();
+    }
 
     // groups: top-2 sum of c per group; all but the `keep` highest leave the ranking
     const int size = experts / groups;
@@ -174,6 +193,7 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
         }
         __syncwarp();
     }
+    if (form & 2) return;                        // the weights are the scores as they are
     const float inv = 1.0f / (sum + 1e-20f);
     for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] *= inv;
 }
@@ -228,7 +248,8 @@ moe_arrange_kernel(const int* ids, int n_pairs, int experts, int tile_rows, int*
     if (xs != nullptr) {
         // a step of few pairs: the activations go into the lists' order here, without a kernel of their own
         __syncthreads();
-        for (int i = threadIdx.x; i < n_pairs * vecs; i += blockDim.x) {
+        const int listed = start[experts];       // pairs whose id names no expert of the lists are in none of them
+        for (int i = threadIdx.x; i < listed * vecs; i += blockDim.x) {
             const int r = i / vecs, c = i % vecs;
             xs[i] = x[(size_t)(order[r] / top) * vecs + c];
         }
@@ -238,10 +259,11 @@ moe_arrange_kernel(const int* ids, int n_pairs, int experts, int tile_rows, int*
 // xs[i, :] = x[order[i] / top, :]: the activations in the order of the list, 16 bytes at a time
 // (width a multiple of 8 bf16).
 __global__ void moe_gather_kernel(const uint4* x, uint4* __restrict__ xs, const int* order,
-                                  int n_pairs, int top, int vecs) {
+                                  int n_pairs, int top, int vecs, const int* listed) {
     let_next_kernel_start();
     wait_for_previous_kernels();
-    const size_t total = (size_t)n_pairs * vecs;
+    // listed: the number of pairs in the lists (the last of the arrange kernel's offsets), where some pairs are in none
+    const size_t total = (size_t)(listed != nullptr ? min(n_pairs, *listed) : n_pairs) * vecs;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int r = (int)(i / vecs), c = (int)(i % vecs);
         xs[i] = x[(size_t)(order[r] / top) * vecs + c];
@@ -251,12 +273,15 @@ __global__ void moe_gather_kernel(const uint4* x, uint4* __restrict__ xs, const 
 // ---- the grouped contractions ------------------------------------------------------------------
 constexpr int GM = 32, GN = 64, GK = 16, G_THREADS = 256;      // a tile of 32 pairs x 64 features; thread: 2 x 4
 
+// gate_form (GATE only): the five constants of another gate than SiLU (`GateForm`), or null.
 // GATE: act[p, n] = silu(sum_k Wg[e][n, k] x[p / top, k]) * (sum_k Wu[e][n, k] x[p / top, k])   (T out)
 // else: y[p, n]   = sum_k Wd[e][n, k] act[p, k]                                                  (float out)
 template <typename T, bool GATE>
 __global__ void __launch_bounds__(G_THREADS)
 moe_grouped_kernel(const T* X, const T* __restrict__ W, const T* __restrict__ W2, void* __restrict__ out_,
-                   const int* offsets, const int* order, const int* tiles, const int* n_tiles, int top, int N, int K) {
+                   const int* offsets, const int* order, const int* tiles, const int* n_tiles, int top, int N, int K,
+                   const float* __restrict__ gate_form) {
+    const GateForm gf = load_gate_form(GATE ? gate_form : nullptr);
     __shared__ float Xs[GK][GM + 1];
     __shared__ float Ws[GK][GN + 1];
     __shared__ float W2s[GATE ? GK : 1][GATE ? GN + 1 : 1];
@@ -319,15 +344,18 @@ moe_grouped_kernel(const T* X, const T* __restrict__ W, const T* __restrict__ W2
             const int n = n0 + tn + b;
             if (n >= N) continue;
             if (GATE)
-                reinterpret_cast<T*>(out_)[(size_t)p * N + n] = from_f32<T>(silu_f32(acc[a][b]) * acc2[a][b]);
+                reinterpret_cast<T*>(out_)[(size_t)p * N + n] = from_f32<T>(gated_f32(acc[a][b], acc2[a][b], gf));
             else
                 reinterpret_cast<float*>(out_)[(size_t)p * N + n] = acc[a][b];
         }
     }
 }
 
+// ids / x / n_real (optional): a chosen id >= n_real hands the token's input row x[t] through instead of a row of y.
+template <typename T>
 __global__ void moe_combine_kernel(float* residual, const float* y, const float* weights, const float* shared_y,
-                                   const float* gate, const int* place, int n_tokens, int width, int top) {
+                                   const float* gate, const int* place, int n_tokens, int width, int top,
+                                   const int* ids, const T* x, int n_real, float scale) {
     let_next_kernel_start();
     wait_for_previous_kernels();
     const size_t total = (size_t)n_tokens * width;
@@ -336,18 +364,23 @@ __global__ void moe_combine_kernel(float* residual, const float* y, const float*
         float acc = 0.f;
         for (int c = 0; c < top; ++c) {
             const size_t p = (size_t)t * top + c;
+            if (ids != nullptr && ids[p] >= n_real) {
+                acc = fmaf(weights[p], to_f32<T>(x[i]), acc);
+                continue;
+            }
             acc = fmaf(weights[p], y[(place != nullptr ? (size_t)place[p] : p) * width + d], acc);
         }
-        if (shared_y != nullptr) acc = fmaf(gate[t], shared_y[i], acc);
-        residual[i] += acc;
+        if (shared_y != nullptr) acc = gate != nullptr ? fmaf(gate[t], shared_y[i], acc) : acc + shared_y[i];
+        residual[i] += scale == 1.f ? acc : scale * acc;
     }
 }
 
 }  // namespace
 
+// form: bit 0 softmax scores instead of sigmoid ones, bit 1 weights not divided by their sum.
 RI_API int ri_moe_route(const void* x, int dtype, const float* router, const float* correction, const float* gate_w,
                         int* ids, float* weights, float* gate_out, int n_tokens, int width, int experts, int top,
-                        int groups, int keep, cudaStream_t stream) {
+                        int groups, int keep, int form, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (experts <= 0 || top <= 0 || top > experts) return fail("moe_route: top %d of %d experts", top, experts);
     if (groups <= 0 || experts % groups || keep <= 0 || keep > groups)
@@ -364,7 +397,7 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
     cudaError_t e;
 #define RI_ROUTE_N(T, V, N) launch_dependent(moe_route_kernel<T, V, N>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)x, \
                                              router, correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top,   \
-                                             groups, keep, per_block)
+                                             groups, keep, per_block, form)
 #define RI_ROUTE(T, V) (per_block == 1 ? RI_ROUTE_N(T, V, 1) : per_block == 2 ? RI_ROUTE_N(T, V, 2) : RI_ROUTE_N(T, V, ROUTE_TOKENS))
     if (dtype == RI_F32) e = vec ? RI_ROUTE(float, true) : RI_ROUTE(float, false);
     else if (dtype == RI_BF16) e = vec ? RI_ROUTE(__nv_bfloat16, true) : RI_ROUTE(__nv_bfloat16, false);
@@ -390,27 +423,28 @@ RI_API int ri_moe_arrange(const int* ids, int n_pairs, int experts, int tile_row
     return check_launch(e, "moe_arrange");
 }
 
-RI_API int ri_moe_gather(const void* x, void* xs, const int* order, int n_pairs, int top, int width, cudaStream_t stream) {
+RI_API int ri_moe_gather(const void* x, void* xs, const int* order, int n_pairs, int top, int width, const int* listed,
+                         cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (width % 8 || (uintptr_t)x % 16 || (uintptr_t)xs % 16) return fail("moe_gather: rows of %d bf16 are not 16-byte runs", width);
     const size_t total = (size_t)n_pairs * (width / 8);
     const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
     cudaError_t e = launch_dependent(moe_gather_kernel, blocks, 256, 0, stream, (const uint4*)x, (uint4*)xs, order, n_pairs,
-                                     top, width / 8);
+                                     top, width / 8, listed);
     return check_launch(e, "moe_gather");
 }
 
 // gate != 0: x [tokens, K], w / w2 [experts, N, K] -> out<dtype> [pairs, N]; else x [pairs, K], w -> out<float> [pairs, N]
 RI_API int ri_moe_grouped_simt(const void* x, const void* w, const void* w2, void* out, int dtype, int gate,
                                const int* offsets, const int* order, const int* tiles, const int* n_tiles, int n_pairs,
-                               int experts, int top, int N, int K, cudaStream_t stream) {
+                               int experts, int top, int N, int K, const float* gate_form, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     const int max_tiles = (n_pairs + GM - 1) / GM + experts;
     dim3 grid(max_tiles, (N + GN - 1) / GN);
     if (grid.y > 65535) return fail("moe_grouped: %d features exceed the grid limit", N);
     cudaError_t e;
 #define RI_GROUPED(T, G) launch_dependent(moe_grouped_kernel<T, G>, grid, G_THREADS, 0, stream, (const T*)x, (const T*)w, \
-                                          (const T*)w2, out, offsets, order, tiles, n_tiles, top, N, K)
+                                          (const T*)w2, out, offsets, order, tiles, n_tiles, top, N, K, gate_form)
     if (dtype == RI_F32) e = gate ? RI_GROUPED(float, true) : RI_GROUPED(float, false);
     else if (dtype == RI_BF16) e = gate ? RI_GROUPED(__nv_bfloat16, true) : RI_GROUPED(__nv_bfloat16, false);
     else return fail("moe_grouped: unknown dtype %d", dtype);
@@ -418,13 +452,25 @@ RI_API int ri_moe_grouped_simt(const void* x, const void* w, const void* w2, voi
     return check_launch(e, "moe_grouped");
 }
 
+// ids, x (dtype x_dtype), n_real: all null / 0, or the chosen ids [tokens, top], the experts' input [tokens, width] and
+// the number of experts with tensors (a chosen id at or beyond it hands x through).  gate may be null with shared_y
+// (the shared result is added as it is).  scale: a factor on everything that is added.
 RI_API int ri_moe_combine(float* residual, const float* y, const float* weights, const float* shared_y, const float* gate,
-                          const int* place, int n_tokens, int width, int top, cudaStream_t stream) {
+                          const int* place, int n_tokens, int width, int top, const int* ids, const void* x, int x_dtype,
+                          int n_real, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if ((ids == nullptr) != (x == nullptr)) return fail("moe_combine: ids and the experts' input go together");
     const size_t total = (size_t)n_tokens * width;
     const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
-    cudaError_t e = launch_dependent(moe_combine_kernel, blocks, 256, 0, stream, residual, y, weights, shared_y, gate,
-                                     place, n_tokens, width, top);
+    cudaError_t e;
+    if (x == nullptr || x_dtype == RI_F32)
+        e = launch_dependent(moe_combine_kernel<float>, blocks, 256, 0, stream, residual, y, weights, shared_y, gate, place,
+                             n_tokens, width, top, ids, (const float*)x, n_real, scale);
+    else if (x_dtype == RI_BF16)
+        e = launch_dependent(moe_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, residual, y, weights, shared_y, gate,
+                             place, n_tokens, width, top, ids, (const __nv_bfloat16*)x, n_real, scale);
+    else
+        return fail("moe_combine: unknown dtype %d", x_dtype);
     return check_launch(e, "moe_combine");
 }
 

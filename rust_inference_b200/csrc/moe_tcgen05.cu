@@ -35,7 +35,13 @@ constexpr int SMEM_BUDGET = 200 * 1024;
 
 enum Status { ST_PRODUCER_TIMEOUT = 31, ST_MMA_TIMEOUT = 32, ST_EPILOGUE_TIMEOUT = 33, ST_DRAIN_TIMEOUT = 34 };
 
-__device__ __forceinline__ float silu_to_bf16(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+// The gate of the gated form (`GateForm`, common.cuh; without constants SiLU(g) * u, bit for bit), with the hardware's
+// fast exponential and division: the result is rounded to bf16 right away.
+__device__ __forceinline__ float gated_to_bf16(float g, float u, const GateForm& f) {
+    g = fminf(g, f.limit);
+    u = fmaxf(fminf(u, f.limit), -f.limit) + f.shift;
+    return __fdividef(g, 1.f + __expf(-f.alpha * g * fmaf(f.cubic * g, g, 1.f))) * u * f.mult;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -47,7 +53,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // out + row * n_feat (rows of a wider matrix, in another order: see the kernel).
 template <bool GATE>
 __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, int f0, int n_feat, bool aligned,
-                                           void* __restrict__ out_, bool spread = false, size_t out_row = 0, int out_ld = 0) {
+                                           void* __restrict__ out_, const GateForm& gf, bool spread = false,
+                                           size_t out_row = 0, int out_ld = 0) {
     constexpr int FEATS = GATE ? TM_ROWS / 2 : TM_ROWS;
     const bool narrow = GATE || spread;                     // the result is bf16
 #pragma unroll 1
@@ -63,7 +70,7 @@ __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, 
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float a = __uint_as_float(v[j]);
-            r[j] = GATE ? silu_to_bf16(a) * __uint_as_float(u[j]) : a;
+            r[j] = GATE ? gated_to_bf16(a, __uint_as_float(u[j]), gf) : a;
         }
         if (aligned && f0 + c0 + 16 <= n_feat) {
             if (narrow) {
@@ -95,7 +102,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out_, const int* offsets,
                       const int* tiles, const int* n_tiles, int n_feat, int K, int stages,
-                      int* status, int spread_groups, int spread_ld) {
+                      int* status, int spread_groups, int spread_ld, const float* __restrict__ gate_form) {
     // spread_groups > 0 (plain form): out is bf16 with rows of spread_ld values, and row i of group e goes to row
     // i * spread_groups + e of it (the groups' rows interleaved: a group is a head, a row a token, and out a matrix
     // [tokens, heads, spread_ld] whose first n_feat channels per head are written).
@@ -228,6 +235,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     } else {
         const int lane_base = (warp & 3) * 32;
         const bool spread = !GATE && spread_groups > 0;
+        const GateForm gf = load_gate_form(GATE ? gate_form : nullptr);       // constants no kernel of the step writes
         const bool aligned = spread ? spread_ld % 8 == 0 : n_feat % 8 == 0;      // rows of `out` keep 16-byte alignment
         for (int i = 0; i < my_tiles; ++i) {
             int e, row0, f0;
@@ -243,7 +251,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (!landed || abort_flag) break;
             const int row = row0 + lane_base + lane;
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * TM_ROWS);
-            write_tile<GATE>(trow, row, row < row_end, f0, n_feat, aligned, out_, spread,
+            write_tile<GATE>(trow, row, row < row_end, f0, n_feat, aligned, out_, gf, spread,
                              spread ? (size_t)(row - offsets[e]) * spread_groups + e : 0, spread_ld);
             tc_fence_before();
             __syncwarp();
@@ -274,7 +282,7 @@ int sm_count() {
 template <bool GATE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, const int* offsets,
            const int* tiles, const int* n_tiles, int n_pairs, int experts, int N, int K, int* status, cudaStream_t stream,
-           int spread_groups = 0, int spread_ld = 0) {
+           int spread_groups = 0, int spread_ld = 0, const float* gate_form = nullptr) {
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     int stages = SMEM_BUDGET / STAGE_BYTES;
     if (stages > total_kb) stages = total_kb;
@@ -290,7 +298,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     long long ctas = sm_count();
     if (ctas > most) ctas = most;
     cudaError_t e = launch_dependent(kernel, dim3((unsigned)ctas), dim3(THREADS), smem, stream, mw, mw2, mx, out, offsets,
-                                     tiles, n_tiles, N, K, stages, status, spread_groups, spread_ld);
+                                     tiles, n_tiles, N, K, stages, status, spread_groups, spread_ld, gate_form);
     return check_launch(e, "moe_grouped_tcgen05");
 }
 
@@ -300,9 +308,10 @@ RI_API int ri_moe_tcgen05_tile_rows() { return TM_TOK; }
 
 // map_x: X [pairs, K] with a box of 128 rows; map_w, map_w2: [experts * N, K] with a box of 128 rows
 // (`ri_gemm_tcgen05_encode` makes them).  offsets / tiles / n_tiles: the arrange kernel's, for tiles of 128 rows.
+// gate_form (gated form only): the five constants of another gate than SiLU, in device memory, or null.
 RI_API int ri_moe_grouped_tcgen05(const void* map_x, const void* map_w, const void* map_w2, void* out, int gate,
                                   const int* offsets, const int* tiles, const int* n_tiles, int n_pairs, int experts, int N,
-                                  int K, int* status, cudaStream_t stream) {
+                                  int K, const float* gate_form, int* status, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (K <= 0 || K % 8) return fail("moe_grouped_tcgen05: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (gate && map_w2 == nullptr) return fail("moe_grouped_tcgen05: the SiLU-gate form needs a second matrix");
@@ -310,7 +319,7 @@ RI_API int ri_moe_grouped_tcgen05(const void* map_x, const void* map_w, const vo
     const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);
     const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
     const CUtensorMap& mw2 = *reinterpret_cast<const CUtensorMap*>(gate ? map_w2 : map_w);
-    if (gate) return launch<true>(mw, mw2, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream);
+    if (gate) return launch<true>(mw, mw2, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream, 0, 0, gate_form);
     return launch<false>(mw, mw2, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream);
 }
 

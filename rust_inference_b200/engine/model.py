@@ -86,10 +86,12 @@ class DecoderModel:
         self.embedding = _build("embedding", self._embedding_spec, **kw)
         self.layers = [_Layer(ls, **kw) for ls in spec.layers]
         self.head = _build("head", self._head_spec, **kw)
+        self.stream_parts = [_build("stream", ps, **kw) for ps in spec.stream_parts]
 
         # the schedule: who writes which cache layer
         seen = set()
         self.schedule = []
+        self._before = []            # per layer run: (stream part, argument) that runs right before it, or None
         self._cache_requests = [None] * spec.cache_layers()
         for entry in spec.schedule:
             if not (0 <= entry.layer < len(self.layers)):
@@ -103,7 +105,10 @@ class DecoderModel:
                 raise ValueError(
                     f"schedule: layer {entry.layer} reads cache {entry.cache}, whose owner keeps "
                     f"{self._cache_requests[entry.cache]}, not {request}")
+            if entry.before is not None and not (0 <= entry.before[0] < len(self.stream_parts)):
+                raise ValueError(f"schedule names stream part {entry.before[0]}, the model has {len(self.stream_parts)}")
             self.schedule.append((entry.layer, entry.cache, writes))
+            self._before.append(entry.before)
 
     # ---- tensors -----------------------------------------------------------
     def _named_parts(self):
@@ -111,6 +116,8 @@ class DecoderModel:
         for layer in self.layers:
             yield from layer.named_parts()
         yield self._head_spec.prefix, self.head
+        for ps, part in zip(self.spec.stream_parts, self.stream_parts):
+            yield ps.prefix, part
 
     def declared_tensors(self) -> dict:
         out = {}
@@ -226,7 +233,12 @@ class DecoderModel:
         records statistics of the hidden state after every layer."""
         residual = ctx.buffer("residual", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx, residual)
+        for part in self.stream_parts:
+            part.begin(residual, ctx)
         for run, (layer, cache_index, writes) in enumerate(self.schedule):
+            before = self._before[run]
+            if before is not None:
+                self.stream_parts[before[0]].forward(residual, ctx, before[1])
             self.layers[layer].block.forward(residual, ctx, cache.layer(cache_index), writes)
             if probe is not None:
                 probe.record(f"L{run}", residual)

@@ -56,8 +56,9 @@ def into_residual(x, w: Weight, residual, ctx):
 
 
 def gated(x, w_gate: Weight, w_up: Weight, out, ctx, form=None):
-    """out<run dtype> = silu(x Wg^T) * (x Wu^T); with `form` (float32 [3] on the device: alpha, limit, shift)
-    out = g' sigmoid(alpha g') (u' + shift), g' = min(x Wg^T, limit), u' = clamp(x Wu^T, -limit, limit)."""
+    """out<run dtype> = silu(x Wg^T) * (x Wu^T); with `form` (`ops.gate_form`: float32 [5] on the device: alpha,
+    limit, shift, cubic, mult) out = mult g' sigmoid(alpha g' (1 + cubic g'^2)) (u' + shift), g' = min(x Wg^T, limit),
+    u' = clamp(x Wu^T, -limit, limit)."""
     if _use_tensor_cores(x, w_gate):
         from . import tcgen05
         return tcgen05.gemm(x, w_gate, out, ops.EPI_SILU_MUL, ctx, w2=w_up, gate_form=form)

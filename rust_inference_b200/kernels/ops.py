@@ -9,6 +9,8 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_int, c_float, c_void_p, c_longlong, c_ulonglong
 
+import math
+
 import torch
 
 from .build import load
@@ -324,11 +326,30 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SILU_MUL, EPI_ACT = 0, 1, 2, 3, 4
 
 
+GELU_TANH_ALPHA = 2.0 * math.sqrt(2.0 / math.pi)      # 0.5 z (1 + tanh(y)) = z sigmoid(2 y)
+GELU_TANH_CUBIC = 0.044715
+
+
+def gate_form(*, alpha: float = 1.0, limit: float = float("inf"), shift: float = 0.0, cubic: float = 0.0,
+              mult: float = 1.0, device="cuda") -> torch.Tensor:
+    """The five constants of the gated epilogue on the device: the gate is
+    mult * g' sigmoid(alpha g' (1 + cubic g'^2)) (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+    The defaults are SiLU(g) * u; GELU_TANH_ALPHA and GELU_TANH_CUBIC make the gate the tanh form of GELU."""
+    return torch.tensor([alpha, limit, shift, cubic, mult], dtype=torch.float32, device=device)
+
+
+def whole_gate_form(form: torch.Tensor) -> torch.Tensor:
+    """A form given as its first three constants (alpha, limit, shift) gets cubic 0 and mult 1."""
+    if form.numel() == 3:
+        return torch.cat([form.reshape(-1), form.new_tensor([0.0, 1.0])])
+    return form
+
+
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
               bias: torch.Tensor | None = None, w2: torch.Tensor | None = None,
               gate_form: torch.Tensor | None = None, act_form: torch.Tensor | None = None) -> torch.Tensor:
     """out = x @ w.T with the chosen epilogue, on the FFMA pipe (float32 accumulate).  gate_form (gated
-    epilogue only): float32 [3] on the device, {alpha, limit, shift} of g' sigmoid(alpha g') (u' + shift) with
+    epilogue only): float32 [5] on the device (`gate_form`; the first three alone are accepted), {alpha, limit, shift, cubic, mult} of mult g' sigmoid(alpha g' (1 + cubic g'^2)) (u' + shift) with
     g' = min(g, limit), u' = clamp(u, -limit, limit); None: SiLU(g) * u.  act_form (EPI_ACT only): float32 [2] on the
     device, the two constants of the learned activation (`xielu`)."""
     _need_cuda(x, w, out, bias, w2)
@@ -343,8 +364,9 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
     if w2 is not None:
         _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "gemm: second matrix")
     if gate_form is not None:
+        gate_form = whole_gate_form(gate_form)
         _need(mode == EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
-              and gate_form.numel() == 3, "gemm: a gate form is three float32 constants of the gated epilogue")
+              and gate_form.numel() == 5, "gemm: a gate form is five float32 constants of the gated epilogue")
         bias = gate_form                      # the gated epilogue takes no bias: its constants travel in that argument
     _need((mode == EPI_ACT) == (act_form is not None), "gemm: the activation epilogue and its constants go together")
     if act_form is not None:
@@ -441,6 +463,38 @@ def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _call("elementwise", "ri_cast", _p(src), c_int(dtype_code(src.dtype)), _p(out), c_int(dtype_code(dtype)),
           c_longlong(src.numel()), _stream())
     return out
+
+
+def stream_add(x: torch.Tensor, other: torch.Tensor | None = None, row: torch.Tensor | None = None) -> torch.Tensor:
+    """x += other + row in place: x float32 [T, width], other the same shape or None, row float32 [width] or None."""
+    _need_cuda(x, other, row)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "stream_add: x must be contiguous float32 [T, width]")
+    _need(other is None or (other.dtype == torch.float32 and other.is_contiguous() and other.shape == x.shape),
+          "stream_add: other must have x's shape")
+    _need(row is None or (row.dtype == torch.float32 and row.is_contiguous() and row.numel() == x.shape[1]),
+          "stream_add: row must be float32 [width]")
+    _call("elementwise", "ri_stream_add", _p(x), _p(other), _p(row), c_int(x.shape[0]), c_int(x.shape[1]), _stream())
+    return x
+
+
+def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor, gate_col: int = 0, factor: float = 1.0) -> torch.Tensor:
+    """x *= sigmoid(gate[:, gate_col : gate_col + width]) * factor in place (float32 arithmetic, one rounding); x
+    contiguous [T, width], gate contiguous [T, >= gate_col + width] of the same dtype."""
+    _need_cuda(x, gate)
+    _need(x.is_contiguous() and gate.is_contiguous() and x.dim() == 2 and gate.dim() == 2 and gate.dtype == x.dtype
+          and gate.shape[0] == x.shape[0] and gate.shape[1] >= gate_col + x.shape[1] and gate_col >= 0,
+          "sigmoid_gate: x [T, width] and gate [T, >= gate_col + width] of one dtype")
+    _call("elementwise", "ri_sigmoid_gate", _p(x), _p(gate), c_int(dtype_code(x.dtype)), c_int(gate.shape[1]), c_int(gate_col),
+          c_int(x.shape[0]), c_int(x.shape[1]), c_float(factor), _stream())
+    return x
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place; x float32, contiguous."""
+    _need_cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and cap > 0, "softcap: contiguous float32 and a positive cap")
+    _call("elementwise", "ri_softcap", _p(x), c_longlong(x.numel()), c_float(cap), _stream())
+    return x
 
 
 def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
@@ -659,16 +713,64 @@ def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, n
     return out
 
 
+def gated_linear_attention(z: torch.Tensor, *, q_col: int, k_col: int, v_col: int, g_col: int, a_col: int, rank: int,
+                           w2: torch.Tensor, bias: torch.Tensor, tau: float, q_scale: float, decay: torch.Tensor,
+                           norm_weight: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor,
+                           out: torch.Tensor, n_seqs: int, heads: int, dim: int, vdim: int, eps: float,
+                           out_scale: float = 1.0, o_raw: torch.Tensor | None = None, piece: int = 0, max_pieces: int = 1,
+                           scratch: torch.Tensor | None = None, longest_run: int = 0) -> torch.Tensor:
+    """The recurrence with a key of its own: per head S <- diag(f) S + k v^T, o = S^T q over every sequence's new tokens
+    in order, with f = sigmoid(w2 a + bias)^(1/tau) per key channel from the low-rank input a, q scaled by q_scale; then
+    o / rms(o) * norm_weight * silu(gate) * out_scale per head.  z: float32 [T, ld] with the columns of q and k
+    ([heads, dim] each), v and the gates ([heads, vdim] each) and a ([rank]) as projected (q is scaled in place); w2:
+    float32 [heads*dim, rank]; decay: float32 [T, heads*dim] scratch; the rest as `gated_recurrence`."""
+    _need_cuda(z, w2, bias, decay, norm_weight, state, cu_seqlens, seq_slot, out, o_raw, scratch)
+    n = z.shape[0]
+    qdim = heads * dim
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2, "gated_linear_attention: z must be float32 [T, ld]")
+    _need(w2.dtype == torch.float32 and w2.is_contiguous() and tuple(w2.shape) == (qdim, rank),
+          "gated_linear_attention: w2 must be float32 [heads*dim, rank]")
+    for t, size in ((bias, qdim), (norm_weight, vdim)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == size, "gated_linear_attention: float32 vectors")
+    _need(decay.dtype == torch.float32 and decay.is_contiguous() and decay.numel() >= n * qdim,
+          "gated_linear_attention: decay must be float32 [T, heads*dim]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "gated_linear_attention: state must be float32 [slots, heads, dim, vdim]")
+    _need(out.is_contiguous() and out.shape == (n, heads * vdim), "gated_linear_attention: out shape")
+    _need(cu_seqlens.dtype == torch.int32 and seq_slot.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
+          and seq_slot.numel() >= n_seqs, "gated_linear_attention: the step's arrays must be int32")
+    if o_raw is None:
+        o_raw = torch.empty((n, heads * vdim), dtype=torch.float32, device=z.device)
+    _need(o_raw.dtype == torch.float32 and o_raw.is_contiguous() and o_raw.numel() >= n * heads * vdim,
+          "gated_linear_attention: o_raw must be float32 [T, heads*vdim]")
+    if piece > 0:
+        need = n_seqs * max_pieces * heads * dim * (vdim + 1)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=z.device)
+        _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+              "gated_linear_attention: scratch too small for the pieces")
+    _call("recurrent", "ri_gated_linear_attention", _p(z), c_int(z.shape[1]), c_int(q_col), c_int(k_col), c_int(v_col),
+          c_int(g_col), c_int(a_col), c_int(rank), _p(w2), _p(bias), c_float(tau), c_float(q_scale), _p(decay),
+          _p(norm_weight), _p(state), _p(cu_seqlens), _p(seq_slot), _p(o_raw), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), c_int(piece),
+          c_int(max_pieces), _p(scratch if piece > 0 else None), c_int(max(0, min(int(longest_run), n))), _stream())
+    global _launches
+    _launches += 5 if piece > 0 else 3
+    return out
+
+
 # ----------------------------------------------------------------------------
 # Routed experts (csrc/moe.cu)
 # ----------------------------------------------------------------------------
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, ids: torch.Tensor,
               weights: torch.Tensor, *, top: int, groups: int = 1, keep: int = 1,
-              gate_weight: torch.Tensor | None = None, gate_out: torch.Tensor | None = None) -> None:
+              gate_weight: torch.Tensor | None = None, gate_out: torch.Tensor | None = None,
+              softmax: bool = False, normalise: bool = True) -> None:
     """Per token the `top` experts with the largest sigmoid(router x) + correction among the `keep` best of
     `groups` groups (a group's score: the sum of its two largest), ids int32 [T, top], and their weights
     float32 [T, top] (the plain sigmoid scores, normalised).  gate_weight float32 [width]: gate_out[t] =
-    sigmoid(gate_weight . x_t) as well."""
+    sigmoid(gate_weight . x_t) as well.  softmax: the scores are softmax(router x) over all experts instead of
+    sigmoids; normalise False: the weights are the chosen scores as they are."""
     _need_cuda(x, router, correction, ids, weights, gate_weight, gate_out)
     n, width = x.shape
     experts = router.shape[0]
@@ -682,7 +784,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, i
               and gate_out.dtype == torch.float32 and gate_out.numel() >= n, "moe_route: gate")
     _call("moe", "ri_moe_route", _p(x), c_int(dtype_code(x.dtype)), _p(router), _p(correction), _p(gate_weight), _p(ids),
           _p(weights), _p(gate_out), c_int(n), c_int(width), c_int(experts), c_int(top), c_int(groups), c_int(keep),
-          _stream())
+          c_int((1 if softmax else 0) | (0 if normalise else 2)), _stream())
 
 
 def moe_tile_rows() -> int:
@@ -714,24 +816,29 @@ def moe_arrange(ids: torch.Tensor, n_pairs: int, experts: int, tile_rows: int, o
           _p(tiles), _p(n_tiles), _p(place), _p(x), _p(xs), c_int(top), c_int(width), _stream())
 
 
-def moe_gather(x: torch.Tensor, xs: torch.Tensor, order: torch.Tensor, *, n_pairs: int, top: int) -> torch.Tensor:
+def moe_gather(x: torch.Tensor, xs: torch.Tensor, order: torch.Tensor, *, n_pairs: int, top: int,
+               listed: torch.Tensor | None = None) -> torch.Tensor:
     """xs[i] = x[order[i] // top]: the activations in the order of the experts' lists (bfloat16 rows of a
-    multiple of 8 values)."""
-    _need_cuda(x, xs, order)
+    multiple of 8 values).  listed (int32 [1] on the device): how many pairs the lists hold, where some are in none."""
+    _need_cuda(x, xs, order, listed)
+    _need(listed is None or listed.dtype == torch.int32, "moe_gather: listed must be int32")
     _need(x.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and x.is_contiguous() and xs.is_contiguous()
           and xs.shape == (n_pairs, x.shape[1]) and x.shape[0] * top >= n_pairs, "moe_gather: shapes")
-    _call("moe", "ri_moe_gather", _p(x), _p(xs), _p(order), c_int(n_pairs), c_int(top), c_int(x.shape[1]), _stream())
+    _call("moe", "ri_moe_gather", _p(x), _p(xs), _p(order), c_int(n_pairs), c_int(top), c_int(x.shape[1]), _p(listed),
+          _stream())
     return xs
 
 
 def moe_grouped_simt(x: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None, out: torch.Tensor, offsets, order,
-                     tiles, n_tiles, *, n_pairs: int, top: int) -> torch.Tensor:
+                     tiles, n_tiles, *, n_pairs: int, top: int, gate_form: torch.Tensor | None = None) -> torch.Tensor:
     """The experts' contractions over the arranged pairs, on the FFMA pipe.  With w2: x [T, K], w and w2
     [experts, N, K], out[p] = silu(w[e] x[p // top]) * (w2[e] x[p // top]) in the run dtype; without:
-    x [pairs, K], out[p] = w[e] x[p] in float32."""
-    _need_cuda(x, w, w2, out, offsets, order, tiles, n_tiles)
+    x [pairs, K], out[p] = w[e] x[p] in float32.  gate_form (`gate_form`, with w2): another gate than SiLU."""
+    _need_cuda(x, w, w2, out, offsets, order, tiles, n_tiles, gate_form)
     experts, n, k = w.shape
     gate = w2 is not None
+    _need(gate_form is None or (gate and gate_form.dtype == torch.float32 and gate_form.numel() == 5),
+          "moe_grouped: a gate form is five float32 constants of the gated form")
     _need(x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and x.shape[1] == k, "moe_grouped: x and w")
     _need(not gate or (w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous()), "moe_grouped: second matrix")
     _need(out.is_contiguous() and out.shape == (n_pairs, n) and out.dtype == (x.dtype if gate else torch.float32),
@@ -739,25 +846,33 @@ def moe_grouped_simt(x: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None, 
     _need(x.shape[0] * (top if gate else 1) >= n_pairs, "moe_grouped: fewer rows than pairs")
     _call("moe", "ri_moe_grouped_simt", _p(x), _p(w), _p(w2), _p(out), c_int(dtype_code(x.dtype)), c_int(1 if gate else 0),
           _p(offsets), _p(order), _p(tiles), _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(top), c_int(n), c_int(k),
-          _stream())
+          _p(gate_form), _stream())
     return out
 
 
 def moe_combine(residual: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, *, top: int,
                 shared_y: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                place: torch.Tensor | None = None) -> None:
-    """residual[t] += sum_c weights[t, c] * y[row of pair t * top + c] (+ gate[t] * shared_y[t]); all float32.
-    A pair's row of y is the pair's own number, or place[pair] when `place` is given."""
-    _need_cuda(residual, y, weights, shared_y, gate, place)
+                place: torch.Tensor | None = None, ids: torch.Tensor | None = None, x: torch.Tensor | None = None,
+                n_real: int = 0, scale: float = 1.0) -> None:
+    """residual[t] += scale * (sum_c weights[t, c] * y[row of pair t * top + c] (+ gate[t] * shared_y[t], or + shared_y[t]
+    without a gate)); sums in float32.  A pair's row of y is the pair's own number, or place[pair] when `place` is given.
+    With ids (int32 [T, top]), x (the experts' input [T, width]) and n_real, a chosen id >= n_real is an expert that hands
+    its input through: its row is x[t]."""
+    _need_cuda(residual, y, weights, shared_y, gate, place, ids, x)
     n, width = residual.shape
     for t in (residual, y, weights, shared_y, gate):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "moe_combine: float32 tensors")
     _need(y.shape == (n * top, width) and weights.numel() >= n * top, "moe_combine: shapes")
     _need(place is None or (place.dtype == torch.int32 and place.numel() >= n * top), "moe_combine: place must be int32 [pairs]")
-    _need((shared_y is None) == (gate is None) and (shared_y is None or (shared_y.shape == (n, width) and gate.numel() >= n)),
-          "moe_combine: the shared result and its gate go together")
+    _need(gate is None or shared_y is not None, "moe_combine: a gate goes with a shared result")
+    _need(shared_y is None or (shared_y.shape == (n, width) and (gate is None or gate.numel() >= n)), "moe_combine: the shared result")
+    _need((ids is None) == (x is None), "moe_combine: ids and the experts' input go together")
+    if ids is not None:
+        _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.numel() >= n * top and x.is_contiguous()
+              and tuple(x.shape) == (n, width), "moe_combine: ids int32 [T, top] and x [T, width]")
     _call("moe", "ri_moe_combine", _p(residual), _p(y), _p(weights), _p(shared_y), _p(gate), _p(place), c_int(n),
-          c_int(width), c_int(top), _stream())
+          c_int(width), c_int(top), _p(ids), _p(x), c_int(dtype_code(x.dtype) if x is not None else RI_F32), c_int(n_real),
+          c_float(scale), _stream())
 
 
 # ---- attention over a shared low-rank latent (csrc/latent.cu) ------------------------------------------

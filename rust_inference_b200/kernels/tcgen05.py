@@ -133,8 +133,9 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
         map_w2 = weight_map(w2)
     if gate_form is not None:
         # the gated epilogue takes no bias: the three constants of its form travel in that argument
+        gate_form = ops.whole_gate_form(gate_form)
         _need(mode == ops.EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
-              and gate_form.numel() == 3, "gemm_tcgen05: a gate form is three float32 constants of the gated epilogue")
+              and gate_form.numel() == 5, "gemm_tcgen05: a gate form is five float32 constants of the gated epilogue")
         bias = gate_form
     _need((mode == ops.EPI_ACT) == (act_form is not None), "gemm_tcgen05: the activation epilogue and its constants go together")
     if act_form is not None:
@@ -175,13 +176,17 @@ def _stacked_map(w: torch.Tensor) -> torch.Tensor:
     return m
 
 
-def grouped_gemm(x: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tiles, n_tiles, *, n_pairs: int):
+def grouped_gemm(x: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tiles, n_tiles, *, n_pairs: int,
+                 gate_form: torch.Tensor | None = None):
     """For every expert e the rows offsets[e]..offsets[e+1] of x [pairs, K] times w[e]^T ([experts, N, K]):
     with w2 out<bf16> = silu(x w[e]^T) * (x w2[e]^T), without out<float32> = x w[e]^T.  `tiles` / `n_tiles` are
-    the arrange kernel's for tiles of GROUPED_TILE_ROWS rows."""
-    _need_cuda(x, w, w2, out, offsets, tiles, n_tiles)
+    the arrange kernel's for tiles of GROUPED_TILE_ROWS rows.  gate_form (`ops.gate_form`, with w2): another gate
+    than SiLU."""
+    _need_cuda(x, w, w2, out, offsets, tiles, n_tiles, gate_form)
     experts, n, k = w.shape
     gate = w2 is not None
+    _need(gate_form is None or (gate and gate_form.dtype == torch.float32 and gate_form.numel() == 5),
+          "grouped_gemm: a gate form is five float32 constants of the gated form")
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
           and x.shape == (n_pairs, k), "grouped_gemm: x must be bf16 [pairs, K]")
     _need(not gate or (w2.shape == w.shape and w2.dtype == torch.bfloat16 and w2.is_contiguous()), "grouped_gemm: second matrix")
@@ -191,7 +196,7 @@ def grouped_gemm(x: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offset
     st = status_word()
     _call("moe_tcgen05", "ri_moe_grouped_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(_stacked_map(w).data_ptr()),
           c_void_p(_stacked_map(w2).data_ptr() if gate else 0), _p(out), c_int(1 if gate else 0), _p(offsets), _p(tiles),
-          _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(n), c_int(k), c_void_p(st.data_ptr()), _stream())
+          _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(n), c_int(k), _p(gate_form), c_void_p(st.data_ptr()), _stream())
     return out
 
 

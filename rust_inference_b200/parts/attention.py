@@ -35,18 +35,20 @@ class GQAttention(Mixer):
     # also holds exp(sink_h), a learned number per head without key or value); `head_gate` (the head's result times
     # sigmoid(W_g x)_h, one more row per head in the projection, `names`: gate); `o_bias` (a bias on the output
     # projection, `names`: o_bias); `own_kv` False: the layer has no key and value projections and attends over the
-    # cache of the layer the schedule gives it, with its own queries.
+    # cache of the layer the schedule gives it, with its own queries.  `out_gate`: the concatenated heads' result is
+    # multiplied element by element with sigmoid(W_g x) before the output projection (one more row per value channel of
+    # every head in the projection, `names`: out_gate).
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
               "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
               "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "o_bias": "o_proj.bias", "sink": "sinks",
-              "gate": "gate_proj.weight", "r1": "distance_r1", "r2": "distance_r2"}
+              "gate": "gate_proj.weight", "r1": "distance_r1", "r2": "distance_r2", "out_gate": "out_gate_proj.weight"}
 
     def __init__(self, *, n_heads: int, n_kv_heads: int, head_dim: int, qkv_bias: bool,
                  position: PartSpec, window: int | None = None, v_head_dim: int | None = None,
                  scale: float | None = None, chunk: int | None = None, out_scale: float = 1.0,
                  names: dict | None = None, qk_norm_eps: float | None = None, values_from_keys: bool = False,
                  softcap: float = 0.0, distance_bias: bool = False, keep_first: int = 0, sink: bool = False,
-                 head_gate: bool = False, o_bias: bool = False, own_kv: bool = True,
+                 head_gate: bool = False, o_bias: bool = False, own_kv: bool = True, out_gate: bool = False,
                  hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if n_heads % n_kv_heads:
@@ -69,7 +71,9 @@ class GQAttention(Mixer):
         self.q_norm = self.k_norm = None
         self.softcap, self.keep_first = float(softcap), int(keep_first or 0)
         self.distance_bias, self.sink, self.head_gate = bool(distance_bias), bool(sink), bool(head_gate)
-        self.o_bias, self.own_kv = bool(o_bias), bool(own_kv)
+        self.o_bias, self.own_kv, self.out_gate = bool(o_bias), bool(own_kv), bool(out_gate)
+        if self.out_gate and self.head_gate:
+            raise ValueError("a gate per head and a gate per channel are not combined")
         if self.softcap < 0 or self.keep_first < 0:
             raise ValueError(f"a score cap and a number of kept positions are not negative, found {softcap}, {keep_first}")
         if self.keep_first and window is None:
@@ -78,7 +82,7 @@ class GQAttention(Mixer):
             raise ValueError("a layer without keys of its own has no key norm and no values taken from keys")
         # what only the general path (one projection, then the position encoding, then attention with these forms) does
         self.extended = bool(self.softcap or self.distance_bias or self.keep_first or self.sink or self.head_gate
-                             or not self.own_kv)
+                             or self.out_gate or not self.own_kv)
         self.sinks = self.dist = self.b_o = None
         self.window = window
         self.chunk = chunk
@@ -103,6 +107,8 @@ class GQAttention(Mixer):
             del specs[nm["k"]], specs[nm["v"]]
         if self.head_gate:
             specs[nm["gate"]] = TensorSpec((self.n_heads, h))
+        if self.out_gate:
+            specs[nm["out_gate"]] = TensorSpec((self.o_dim, h))
         if self.sink:
             specs[nm["sink"]] = TensorSpec((self.n_heads,), role="vector", init="zeros")
         if self.distance_bias:
@@ -126,8 +132,9 @@ class GQAttention(Mixer):
         mats = [tensors[nm["q"]]]
         if self.own_kv:
             mats += [tensors[nm["k"]]] + ([] if self.values_from_keys else [tensors[nm["v"]]])
-        if self.head_gate:
-            mats.append(tensors[nm["gate"]])           # one more row per head: the gates come out of the same product
+        if self.head_gate or self.out_gate:
+            # one more row per head (or per value channel of every head): the gates come out of the same product
+            mats.append(tensors[nm["gate" if self.head_gate else "out_gate"]])
             rows = sum(m.shape[0] for m in mats)
             if rows % 8:                               # rows of zeros keep a token's row a multiple of 16 bytes, which the
                 mats.append(torch.zeros(-rows % 8, mats[0].shape[1], dtype=mats[0].dtype, device=mats[0].device))   # tensor-core kernels want
@@ -161,6 +168,8 @@ class GQAttention(Mixer):
                 at += self.v_dim
         if self.head_gate:
             out[nm["gate"]] = w[at:at + self.n_heads]
+        if self.out_gate:
+            out[nm["out_gate"]] = w[at:at + self.o_dim]
         if self.sink:
             out[nm["sink"]] = self.sinks
         if self.distance_bias:
@@ -220,10 +229,13 @@ class GQAttention(Mixer):
         attn_kernels.attention(qkv, cache_layer, mixed, ctx, n_heads=self.n_heads,
                                n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,
                                window=self.window or 0, chunk=self.chunk or 0, v_head_dim=self.v_head_dim,
-                               out_scale=self.out_scale, softcap=self.softcap, keep_first=self.keep_first,
-                               sink=self.sinks, dist=self.dist,
+                               out_scale=1.0 if self.out_gate else self.out_scale, softcap=self.softcap,
+                               keep_first=self.keep_first, sink=self.sinks, dist=self.dist,
                                gate=qkv[:, gate_col:gate_col + self.n_heads] if self.head_gate else None)
+        from ..kernels import ops
+        if self.out_gate:
+            # the gates of the projection's last columns, the mixer's factor with them (float32, one rounding)
+            ops.sigmoid_gate_(mixed, qkv, gate_col, self.out_scale)
         linear.into_residual(mixed, self.w_o, residual, ctx)
         if self.o_bias:
-            from ..kernels import ops
             ops.add_row_bias(residual, self.b_o_scaled)

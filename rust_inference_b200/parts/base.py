@@ -131,6 +131,18 @@ class DepthMix(Part):
         return None
 
 
+class StreamStep(Part):
+    """Something that happens to the whole stream between layers, at places the schedule names (`ScheduleEntry.before`):
+    `begin` is called once per step when the embedding has filled the stream, `forward` right before the layer run that
+    names the part, with the argument the schedule gives (which pass of a loop begins, for instance)."""
+
+    def begin(self, stream: torch.Tensor, ctx) -> None:
+        pass
+
+    def forward(self, stream: torch.Tensor, ctx, arg: int) -> None:
+        raise NotImplementedError
+
+
 class Arrangement:
     """How a layer's parts are wired.  Built from the already-built parts, one per role.
 

@@ -1,6 +1,6 @@
 """The output head: final norm, then logits = W h in float32, on the wanted rows only
 (transformer.rs:89, :97).  The matrix is the embedding's when the model ties them: the same
-storage, where the reference clones it (model.rs:221-226)."""
+storage, where the reference clones it (model.rs:221-226).  `softcap` > 0: logits <- softcap * tanh(logits / softcap)."""
 from __future__ import annotations
 
 import torch
@@ -14,10 +14,13 @@ from .spec import PartSpec, TensorSpec
 @register("head", "linear_head")
 class LinearHead(Head):
     def __init__(self, *, vocab_size: int, norm: PartSpec, tied: bool, weight_prefix: str | None = "lm_head.",
-                 weight_name: str = "weight", hidden_size: int, dtype, device):
+                 weight_name: str = "weight", softcap: float = 0.0, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         self.vocab_size = vocab_size
         self.wants_tie = bool(tied)
+        self.softcap = float(softcap or 0.0)
+        if self.softcap < 0:
+            raise ValueError(f"a cap on the logits is not negative, found {softcap}")
         self.weight_prefix = weight_prefix
         self.weight_name = weight_name      # the matrix is the tensor weight_prefix + weight_name
         self.norm_prefix = norm.prefix
@@ -63,4 +66,7 @@ class LinearHead(Head):
         if logits_out is None:
             logits_out = torch.empty((ctx.n_logit_rows, self.vocab_size), dtype=torch.float32, device=residual.device)
         linear.logits(normed, self.weight, logits_out, ctx)
+        if self.softcap:
+            from ..kernels import ops
+            ops.softcap_(logits_out, self.softcap)
         return logits_out

@@ -13,12 +13,13 @@ Interfaces (see `parts.base`):
   embedding         Embedding (token ids -> hidden stream)
   head              Head (hidden stream -> logits)
   depth             DepthMix (what a layer hands on, as a function of the results of all layers so far)
+  stream            StreamStep (something that happens to the whole stream between layer runs the schedule names)
 """
 from __future__ import annotations
 
 _REGISTRIES: dict[str, dict] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
-    "depth": {},
+    "depth": {}, "stream": {},
 }
 
 
@@ -57,3 +58,4 @@ def _ensure_builtin() -> None:
     from . import norm, rope, attention, feed_forward, block, embedding, head  # noqa: F401
     from . import recurrence, parallel_mixer, routed_experts, latent_attention  # noqa: F401
     from . import depth, state_space, delta_rule  # noqa: F401
+    from . import linear_attention, loop  # noqa: F401

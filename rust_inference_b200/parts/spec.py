@@ -59,9 +59,12 @@ class ScheduleEntry:
     cache       which cache layer its mixer uses.  Entries that name the same `cache`
                 share keys/values (or state): the first of them in the schedule writes
                 it, the later ones only read it;
+    before      (index into `ModelSpec.stream_parts`, argument) or None: that part's `forward(stream, ctx, argument)`
+                runs on the stream right before this layer run.
     """
     layer: int
     cache: int
+    before: tuple | None = None
 
 
 @dataclass(frozen=True)
@@ -86,6 +89,8 @@ class ModelSpec:
     stop_ids: tuple = ()
     embedding: PartSpec | None = None
     head: PartSpec | None = None
+    # parts of the category "stream" that act on the whole stream between layer runs (`ScheduleEntry.before`)
+    stream_parts: tuple = ()
 
     def embedding_part(self) -> PartSpec:
         if self.embedding is not None:
