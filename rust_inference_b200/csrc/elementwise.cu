@@ -850,9 +850,12 @@ RI_API int ri_rope_normed_cache_write(void* qkv, int dtype, int ld, const float*
                                       int page_size, int style, int write_kv, int rot, int v_hd, int v_from_k,
                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rot <= 0) rot = hd;
+    const bool unrotated = rot < 0;       // rot < 0: nothing is rotated (no tables); 0: the whole head
+    if (unrotated) rot = 0;
+    else if (rot == 0) rot = hd;
     if (v_hd <= 0) v_hd = hd;
     if (rot % 2 || rot > hd) return fail("rope_normed_cache_write: %d rotated channels of a head of %d", rot, hd);
+    if (!unrotated && (cos_t == nullptr || sin_t == nullptr)) return fail("rope_normed_cache_write: a rotation needs its tables");
     if (style != 0 && style != 1) return fail("rope_normed_cache_write: unknown style %d", style);
     if (v_from_k && v_hd != hd) return fail("rope_normed_cache_write: values taken from keys of %d have the size %d", hd, v_hd);
     const size_t smem = (size_t)NORMED_ROPE_WARPS * hd * sizeof(float);
@@ -867,7 +870,7 @@ RI_API int ri_rope_normed_cache_write(void* qkv, int dtype, int ld, const float*
                          (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 &&
                          (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0 && (q_w == nullptr || (uintptr_t)q_w % 16 == 0) &&
                          (k_w == nullptr || (uintptr_t)k_w % 16 == 0);
-    if (dtype == RI_BF16 && aligned && pairing_ok) {
+    if (dtype == RI_BF16 && aligned && pairing_ok && !unrotated) {
         e = launch_dependent(rope_normed_cache_write_vec_kernel, blocks, NORMED_ROPE_WARPS * 32, 0, stream, (__nv_bfloat16*)qkv, ld,
                              cos_t, sin_t, q_w, k_w, eps, token_pos, token_seq, seq_slot, page_table, max_pages,
                              (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_tokens, n_heads, n_kv_heads, hd, page_size, style,

@@ -239,10 +239,10 @@ def rope_normed_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Ten
     v_hd = head_dim if v_head_dim is None else int(v_head_dim)
     cols = (n_heads + n_kv_heads) * head_dim + (0 if values_from_keys else n_kv_heads * v_hd)
     _need(qkv.is_contiguous() and qkv.shape[1] >= cols, "rope_normed_cache_write: qkv holds too few columns")
-    _need(0 < rot <= head_dim and rot % 2 == 0, "rope_normed_cache_write: rotated channels must be even and at most head_dim")
+    _need(0 <= rot <= head_dim and rot % 2 == 0, "rope_normed_cache_write: rotated channels must be even and at most head_dim")
     _need(not values_from_keys or v_hd == head_dim, "rope_normed_cache_write: values taken from the keys have their size")
-    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
-          and cos.is_contiguous() and sin.is_contiguous(),
+    _need(rot == 0 or (cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
+                       and cos.is_contiguous() and sin.is_contiguous()),
           "rope_normed_cache_write: tables must be float32 [positions, rotated channels / 2]")
     for w in (q_weight, k_weight):
         _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == head_dim),
@@ -255,7 +255,7 @@ def rope_normed_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Ten
     _call("elementwise", "ri_rope_normed_cache_write", _p(qkv), c_int(dtype_code(qkv.dtype)), c_int(qkv.shape[1]),
           _p(cos), _p(sin), _p(q_weight), _p(k_weight), c_float(eps), _p(token_pos), _p(token_seq), _p(seq_slot),
           _p(page_table), c_int(page_table.shape[1]), _p(kcache), _p(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads),
-          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), c_int(rot), c_int(v_hd),
+          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), c_int(rot if rot else -1), c_int(v_hd),
           c_int(1 if values_from_keys else 0), _stream())
 
 

@@ -1,6 +1,6 @@
 """The Belizen decoder as a `ModelSpec`.
 
-Every layer is pre-norm with a factor m on both branches (`pre_norm`; the parts' `out_scale`):
+Every layer is pre-norm with a factor m on both branches (`pre_norm_optional_ff`; the parts' `out_scale`):
 x <- x + m mixer(n1(x)), then x <- x + m ff(n2(x)), RMS norms with plain weights.  The mixer is one of
 
 * `attention`: grouped-query attention with projection biases, queries and keys RMS-normed per head and rotated in the
@@ -88,7 +88,7 @@ def build_spec(cfg: BelizenConfig) -> ModelSpec:
                     "shared_size": f.shared_ff, "shared_form": None if f.shared_ff is None else {"limit": f.shared_limit},
                     "shared_gate": False, "out_scale": m, "names": _EXPERT_NAMES}, prefix="mlp.")
             parts["feed_forward"], parts["feed_forward_norm"] = ff, _norm("norm2", eps)
-        layers.append(LayerSpec(prefix=f"l{i}.", arrangement="pre_norm", parts=parts))
+        layers.append(LayerSpec(prefix=f"l{i}.", arrangement="pre_norm_optional_ff", parts=parts))
     stream_parts = ()
     if cfg.loop is not None:
         stream_parts = (PartSpec("pass_entry", {"passes": cfg.loop.times, "readd_input": True, "weight_name": "step"},

@@ -11,16 +11,9 @@ from .registry import register
 @register("arrangement", "pre_norm")
 class PreNorm(Arrangement):
     """h1 = x + mixer(norm(x)); h2 = h1 + ff(norm(h1)): the un-normalised stream is carried
-    (transformer.rs:31-47).  Roles: mixer, feed_forward, mixer_norm, feed_forward_norm.  A layer may have no
-    feed-forward (and then no norm for it)."""
+    (transformer.rs:31-47).  Roles: mixer, feed_forward, mixer_norm, feed_forward_norm."""
 
     ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
-    OPTIONAL = ("feed_forward", "feed_forward_norm")
-
-    def __init__(self, **parts):
-        super().__init__(**parts)
-        if (self.feed_forward is None) != (self.feed_forward_norm is None):
-            raise ValueError("pre_norm: a feed-forward comes with its norm, and the norm with it")
 
     def forward(self, residual, ctx, cache_layer, writes_cache):
         normed = ctx.buffer("normed", (residual.shape[0], residual.shape[1]), ctx.dtype)
@@ -30,6 +23,18 @@ class PreNorm(Arrangement):
             return
         self.feed_forward_norm.forward(residual, normed)
         self.feed_forward.forward(normed, residual, ctx)
+
+
+@register("arrangement", "pre_norm_optional_ff")
+class PreNormOptionalFeedForward(PreNorm):
+    """The same for models whose layers may have no feed-forward (and then no norm for it)."""
+
+    OPTIONAL = ("feed_forward", "feed_forward_norm")
+
+    def __init__(self, **parts):
+        super().__init__(**parts)
+        if (self.feed_forward is None) != (self.feed_forward_norm is None):
+            raise ValueError("pre_norm_optional_ff: a feed-forward comes with its norm, and the norm with it")
 
 
 @register("arrangement", "parallel_two_norms")

@@ -154,3 +154,12 @@ class Unrotated(PositionEncoding):
         ops.rope_cache_write(qkv, None, None, ctx.token_pos, ctx.token_seq, ctx.seq_slot, ctx.page_table, cache_layer.k,
                              cache_layer.v, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
                              page_size=ctx.page_size, style=0, write_kv=True, rot_dims=0, v_head_dim=v_head_dim)
+
+    def apply_normed_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv, q_weight,
+                               k_weight, eps, values_from_keys=False, v_head_dim=None):
+        """The RMS norm of every q and k head (weights shared by the heads; None: no norm) without any rotation; keys
+        and values go into the cache."""
+        ops.rope_normed_cache_write(qkv, None, None, q_weight, k_weight, eps, ctx.token_pos, ctx.token_seq, ctx.seq_slot,
+                                    ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                                    head_dim=head_dim, page_size=ctx.page_size, style=0, write_kv=write_kv, rot_dims=0,
+                                    v_head_dim=v_head_dim, values_from_keys=values_from_keys)

@@ -195,6 +195,14 @@ def forward(cfg, w, tokens, dtype=torch.float64, layers_out=None):
     return cap * torch.tanh(logits / cap) if cap else logits
 
 
+def greedy(cfg, w, prompt, n_new):
+    """The n_new tokens with the largest logit, one after another, the whole sequence recomputed for each."""
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(torch.argmax(forward(cfg, w, tokens)[-1])))
+    return tokens[len(prompt):]
+
+
 def tensor_shapes(cfg):
     """Name -> shape of every tensor a model of this configuration has."""
     D = cfg["width"]
