@@ -5,6 +5,7 @@
     python bench.py --arch lulisun [--arch-sizes 1k|2k|4k]     (another model beside the dense decoder; see below)
     python bench.py --arch vadodra [--arch-sizes 1k|2k|4k]     (likewise)
     python bench.py --arch redodra [--arch-sizes 1k|2k|4k]     (likewise, beside a Lulisun-style model too)
+    python bench.py --arch belizen [--arch-sizes 1k|2k|4k]     (likewise)
 
 Default run: a Qwen2.5-7B-sized dense decoder (28 layers, hidden 3584, 28 heads, 4 kv
 heads, head_dim 128, intermediate 18944, vocabulary 152064, q/k/v biases, untied head)
@@ -38,6 +39,9 @@ attention whose values are the unrotated keys, attention over a shared latent, a
 `rust_inference_b200/kernels/vadodra_bench.py`).  `--arch redodra` does it for a Redodra-style model (window attention with kept
 first positions beside a state space, causal attention with a sink and a gate, the gated delta rule, a learned activation)
 beside a Lulisun-style model and a dense decoder of equal size (`rust_inference_b200/kernels/redodra_bench.py`).
+`--arch belizen` does it for a Belizen-style model (window attention with kept first positions, normed and rotated heads and
+a gate on the result; gated linear attention; routed experts with pass-through ones; a run of layers passed again) beside the
+same two (`rust_inference_b200/kernels/belizen_bench.py`).
 
 Prints ONE JSON line.  Only one GPU is used: for --gpus > 1 it says so and exits with 2.
 """
@@ -197,10 +201,10 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=8, help="with --kernel: tokens in the step")
     ap.add_argument("--context", type=int, default=1024, help="with --kernel: cached positions per sequence")
     ap.add_argument("--once", action="store_true", help="with --kernel: launch the workload once, untimed (for ncu)")
-    ap.add_argument("--arch", default="dense", choices=["dense", "lulisun", "vadodra", "redodra"],
+    ap.add_argument("--arch", default="dense", choices=["dense", "lulisun", "vadodra", "redodra", "belizen"],
                     help="lulisun / vadodra / redodra: prefill and decode throughput of a model of that design beside a dense decoder of "
                          "equal size, kernel by kernel against the rooflines, instead of the default workload")
-    ap.add_argument("--arch-sizes", default="2k", choices=["1k", "2k", "4k"], help="with --arch lulisun / vadodra / redodra: the layer sizes")
+    ap.add_argument("--arch-sizes", default="2k", choices=["1k", "2k", "4k"], help="with --arch lulisun / vadodra / redodra / belizen: the layer sizes")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -231,6 +235,12 @@ def main() -> int:
         from rust_inference_b200.kernels import redodra_bench
         peaks, peak_source = load_peaks()
         return redodra_bench.main(args.arch_sizes, peaks, peak_source, prefill_tokens=max(1, args.prefill_tokens),
+                                  batch=args.batch, context=args.context if args.context != 1024 else None,
+                                  steps=max(1, min(args.steps, 64)))
+    if args.arch == "belizen":
+        from rust_inference_b200.kernels import belizen_bench
+        peaks, peak_source = load_peaks()
+        return belizen_bench.main(args.arch_sizes, peaks, peak_source, prefill_tokens=max(1, args.prefill_tokens),
                                   batch=args.batch, context=args.context if args.context != 1024 else None,
                                   steps=max(1, min(args.steps, 64)))
     warmup = max(3, args.warmup)

@@ -23,6 +23,13 @@
 // softmax computes its exponentials before it waits for P V of the page before (it needs that only
 // to overwrite P and to rescale O).  Two CTAs fit on an SM (96 KiB of shared memory, 256 TMEM columns).
 //
+// Two further forms of the score and the mask (template FORMS; the plain kernel is compiled without them and is what it
+// was): capped scores, s <- cap * tanh(s * scale / cap), formed by the softmax thread in the base-2 domain before the
+// maximum is taken (tanh(x) = 1 - 2 / (1 + 2^(2 x log2 e)), the hardware's exponential and division, relative error far
+// below the bf16 rounding of P); and, with a window, the sequence's first `keep_first` positions kept visible: the page
+// walk then starts with the pages before the window that hold kept positions, and the mask lets keys below keep_first
+// pass.
+//
 // All mbarrier waits are bounded; on a timeout the kernel records a code in the host-visible
 // status word and winds down.
 #include "tcgen05_common.cuh"
@@ -83,13 +90,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
+template <int HD, bool FORMS>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int max_pages,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                        const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale_log2, int window,
-                       float out_scale, __nv_bfloat16* __restrict__ out, int out_ld, uint32_t smem_bytes, int* status) {
+                       float out_scale, __nv_bfloat16* __restrict__ out, int out_ld, uint32_t smem_bytes, int* status,
+                       float cap_log2, float scale_over_cap, int keep_first) {
     constexpr int ATOMS = HD / 64;                       // 64-wide (128-byte) column tiles per row of head_dim
     constexpr int Q_BYTES = ATOMS * BM * 128;            // [atom][128 queries][64]
     constexpr int K_BYTES = ATOMS * BN * 128;            // one buffer: [atom][64 keys][64]
@@ -123,7 +131,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
     // `window` is a span (common.cuh: first_visible_key): > 0 the last keys, < 0 the query's own block of positions
     const int first_key = first_visible_key(pos_lo, window);
-    const int pg_begin = first_key / BN, n_pages = pos_hi / BN + 1 - pg_begin;
+    const int pg_begin = first_key / BN;
+    // FORMS: the pages before the window's that hold kept first positions are walked first
+    const int kept_pages = (FORMS && keep_first > 0 && window > 0) ? min((keep_first + BN - 1) / BN, pg_begin) : 0;
+    const int n_pages = pos_hi / BN + 1 - pg_begin + kept_pages;
+    auto page_index = [&](int j) { return j < kept_pages ? j : pg_begin + (j - kept_pages); };
 
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -171,10 +183,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int a = 0; a < ATOMS; ++a)
                 tma_load_2d(q_smem + a * BM * 128, &map_q, smem_u32(&q_full), h * HD + a * 64, tok0 + q0);
             int k_issued = 0, v_issued = 0;
-            int page_next = pages[pg_begin];                        // a page's number is fetched one turn ahead
+            int page_next = pages[page_index(0)];                   // a page's number is fetched one turn ahead
             for (int j = 0; j < n_pages; ++j) {
                 const int row = (page_next * n_kv_heads + kvh) * BN;
-                if (j + 1 < n_pages) page_next = pages[pg_begin + j + 1];
+                if (j + 1 < n_pages) page_next = pages[page_index(j + 1)];
                 const int kb = j & 1;
                 if (!mbar_wait(smem_u32(&k_empty[kb]), (uint32_t)((j >> 1) & 1) ^ 1u) || abort_flag) {
                     report(status, ST_ATTN_PRODUCER); abort_flag = 1; break;
@@ -265,12 +277,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < BN; c += 16) tmem_ld16(trow + S_COL + (j & 1) * BN + c, sv + c);
             tmem_wait_ld();
-            const int key0 = (pg_begin + j) * BN;
+            const int key0 = page_index(j) * BN;
+            if (FORMS && cap_log2 > 0.f) {
+                // capped scores, already in the base-2 domain: cap log2(e) tanh(s scale / cap)
+                const float two_x = 2.f * 1.4426950408889634f * scale_over_cap;
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const float e = fast_exp2(__uint_as_float(sv[c]) * two_x);
+                    sv[c] = __float_as_uint(cap_log2 * (1.f - __fdividef(2.f, 1.f + e)));
+                }
+            }
+            const float eff_scale = (FORMS && cap_log2 > 0.f) ? 1.f : scale_log2;
             // The maximum is taken over the raw scores (the scale is positive), and scale and maximum
             // are folded into one multiply-add per score: p = 2^(s * scale_log2 - m).
             float mx_raw = -INFINITY;
             // pages that every row of the warp sees whole need no mask
-            const bool whole = key0 + BN - 1 <= pos_lo + lane_base && key0 >= first_visible_key(pos_lo + lane_base + 31, window);
+            const bool whole = (FORMS && j < kept_pages)
+                ? key0 + BN - 1 < keep_first
+                : key0 + BN - 1 <= pos_lo + lane_base && key0 >= first_visible_key(pos_lo + lane_base + 31, window);
             if (whole) {
 #pragma unroll
                 for (int c = 0; c < BN; c += 2)
@@ -279,12 +303,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = key0 + c;
-                    const bool vis = key <= pos && key >= first_vis;
+                    const bool vis = key <= pos && (key >= first_vis || (FORMS && key < keep_first));
                     if (!vis) sv[c] = 0xff800000u;              // -inf
                     mx_raw = fmaxf(mx_raw, __uint_as_float(sv[c]));
                 }
             }
-            const float mx = mx_raw * scale_log2;                // -inf stays -inf
+            const float mx = mx_raw * eff_scale;                 // -inf stays -inf
             // move the scaling maximum only when the true one ran ahead of it by more than 2^8
             const bool move = mx > m_used + (float)RESCALE_LOG2;
             const float m_new = move ? mx : m_used;
@@ -292,7 +316,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float neg_mref = (m_new == -INFINITY) ? 0.f : -m_new;   // nothing visible yet: every p is 0
             // the exponentials do not need the previous P V product; everything after this does
             // two scores at a time through the packed float32 pipe (one FMA and one ADD per pair)
-            const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(neg_mref, neg_mref);
+            const float2 scale2 = make_float2(eff_scale, eff_scale), shift2 = make_float2(neg_mref, neg_mref);
             float2 sum2 = make_float2(0.f, 0.f);
             uint32_t pk[BN / 2];
 #pragma unroll
@@ -376,16 +400,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
-template <int HD>
+template <int HD, bool FORMS>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, int max_pages,
            const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new, int n_heads,
-           int n_kv_heads, float scale, int window, float out_scale, void* out, int out_ld, int* status, cudaStream_t stream) {
+           int n_kv_heads, float scale, int window, float out_scale, void* out, int out_ld, int* status, cudaStream_t stream,
+           float softcap = 0.f, int keep_first = 0) {
     constexpr int ATOMS = HD / 64;
     // Q, two K and two V pages, P, the barriers; with head_dim 128 no room for alignment padding is left if
     // two CTAs are to share an SM (the kernel refuses, with a status code, a shared window that needs any)
     constexpr int TILES = ATOMS * BM * 128 + 4 * ATOMS * BN * 128;
     constexpr int SMEM = TILES + (HD >= 128 ? 256 : 1024 + 256);
-    auto kernel = attn_prefill_tc_kernel<HD>;
+    auto kernel = attn_prefill_tc_kernel<HD, FORMS>;
     static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
     if (int rc = raise_dynamic_smem(kernel, SMEM, configured, "attention_tcgen05")) return rc;
     // blocks are handed out x fastest: every head and sequence of the longest query tiles first, the short
@@ -394,7 +419,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv, page_table, max_pages,
                                      seq_slot, seq_start, cu_seqlens, n_heads, n_kv_heads, scale_log2, window,
-                                     out_scale, (__nv_bfloat16*)out, out_ld, (uint32_t)SMEM, status);
+                                     out_scale, (__nv_bfloat16*)out, out_ld, (uint32_t)SMEM, status,
+                                     softcap * 1.4426950408889634f, softcap > 0.f ? scale / softcap : 0.f, keep_first);
     return check_launch(e, "attention_tcgen05");
 }
 
@@ -433,10 +459,36 @@ RI_API int ri_attention_tcgen05_prefill(const void* map_q, const void* map_k, co
     const CUtensorMap& mk = *reinterpret_cast<const CUtensorMap*>(map_k);
     const CUtensorMap& mv = *reinterpret_cast<const CUtensorMap*>(map_v);
     if (hd == 64)
-        return launch<64>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
-                          n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
-    return launch<128>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
-                       n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
+        return launch<64, false>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
+                                 n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
+    return launch<128, false>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
+                              n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
+}
+
+// The same with capped scores (softcap > 0: s <- softcap tanh(s scale / softcap)) and, with a window (> 0 only: the last
+// so many keys), the sequence's first keep_first positions kept visible beyond it.
+RI_API int ri_attention_tcgen05_prefill_forms(const void* map_q, const void* map_k, const void* map_v, const int* page_table,
+                                              int max_pages, const int* seq_slot, const int* seq_start,
+                                              const int* cu_seqlens, void* out, int out_ld, int n_seqs, int max_new,
+                                              int n_heads, int n_kv_heads, int hd, int page_size, float scale, int window,
+                                              float out_scale, float softcap, int keep_first, int* status,
+                                              cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (!ri_attention_tcgen05_supports(hd, page_size, n_heads, n_kv_heads, 8, out_ld))
+        return fail("attention_tcgen05: head_dim %d, pages of %d, %d heads over %d kv heads, out rows of %d are not supported",
+                    hd, page_size, n_heads, n_kv_heads, out_ld);
+    if (softcap < 0.f || keep_first < 0 || window < 0 || (keep_first > 0 && window == 0))
+        return fail("attention_tcgen05: a cap of %f, %d kept positions, a window of %d", (double)softcap, keep_first, window);
+    if ((uintptr_t)out % 16) return fail("attention_tcgen05: out is not 16-byte aligned");
+    if (n_heads > 65535 || n_seqs > 65535) return fail("attention_tcgen05: %d heads / %d sequences exceed the grid limit", n_heads, n_seqs);
+    const CUtensorMap& mq = *reinterpret_cast<const CUtensorMap*>(map_q);
+    const CUtensorMap& mk = *reinterpret_cast<const CUtensorMap*>(map_k);
+    const CUtensorMap& mv = *reinterpret_cast<const CUtensorMap*>(map_v);
+    if (hd == 64)
+        return launch<64, true>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
+                                n_kv_heads, scale, window, out_scale, out, out_ld, status, stream, softcap, keep_first);
+    return launch<128, true>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
+                             n_kv_heads, scale, window, out_scale, out, out_ld, status, stream, softcap, keep_first);
 }
 
 RI_DEFINE_LAST_ERROR()

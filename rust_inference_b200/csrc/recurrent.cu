@@ -301,16 +301,22 @@ __global__ void headwise_rmsnorm_kernel(const float* x, int ld, int col0, const 
     }
 }
 
-// The keyed form's decays and queries, every token at once.  A block takes PREP_TOKENS tokens: their low-rank inputs
-// a = z[t, a_col ..] (rank values each) go to shared memory, and thread c reads row c of W2 once for all of them:
+// The keyed form's decays and queries, every token at once.  A block takes PREP_TOKENS tokens and PREP_CHANNELS key
+// channels: the tokens' low-rank inputs a = z[t, a_col ..] (rank values each) go to shared memory, and a thread reads its
+// channel's row of W2 once for all of them (16 bytes at a time where the rank allows):
 //     decay[t, c] = sigmoid(b[c] + W2[c, :] . a_t)^(1/tau) = exp(log_sigmoid(.) / tau),       z[t, q_col + c] *= q_scale
 // log_sigmoid(x) = min(x, 0) - log1p(exp(-|x|)): no overflow on either side, and no 1 - tiny for decays near 1.
+// A decode step's few tokens are spread over the SMs by the channels.
 constexpr int PREP_TOKENS = 8;
-__global__ void __launch_bounds__(256)
+constexpr int PREP_CHANNELS = 128;
+template <bool VEC>
+__global__ void __launch_bounds__(PREP_CHANNELS)
 keyed_prepare_kernel(float* z, int ld, int q_col, int a_col, int rank, const float* __restrict__ w2,
                      const float* __restrict__ bias, float inv_tau, float q_scale, float* __restrict__ decay, int n_tokens,
                      int qdim) {
-    extern __shared__ float a_sh[];                              // [PREP_TOKENS][rank]
+    extern __shared__ __align__(16) float a_sh[];                // [PREP_TOKENS][rank]
+    const int c = blockIdx.y * PREP_CHANNELS + threadIdx.x;
+    const float b = c < qdim ? bias[c] : 0.f;
     let_next_kernel_start();
     wait_for_previous_kernels();
     const int t0 = blockIdx.x * PREP_TOKENS;
@@ -320,25 +326,34 @@ keyed_prepare_kernel(float* z, int ld, int q_col, int a_col, int rank, const flo
         a_sh[i] = k < n_here ? z[(size_t)(t0 + k) * ld + a_col + r] : 0.f;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < qdim; c += blockDim.x) {
-        float acc[PREP_TOKENS];
-        const float b = bias[c];
+    if (c >= qdim) return;
+    float acc[PREP_TOKENS];
 #pragma unroll
-        for (int k = 0; k < PREP_TOKENS; ++k) acc[k] = b;
-        const float* w = w2 + (size_t)c * rank;
+    for (int k = 0; k < PREP_TOKENS; ++k) acc[k] = b;
+    const float* w = w2 + (size_t)c * rank;
+    if (VEC) {
+        for (int r = 0; r < rank; r += 4) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + r);
+#pragma unroll
+            for (int k = 0; k < PREP_TOKENS; ++k) {
+                const float4 av = *reinterpret_cast<const float4*>(a_sh + k * rank + r);
+                acc[k] = fmaf(wv.x, av.x, fmaf(wv.y, av.y, fmaf(wv.z, av.z, fmaf(wv.w, av.w, acc[k]))));
+            }
+        }
+    } else {
         for (int r = 0; r < rank; ++r) {
             const float wv = w[r];
 #pragma unroll
             for (int k = 0; k < PREP_TOKENS; ++k) acc[k] = fmaf(wv, a_sh[k * rank + r], acc[k]);
         }
+    }
 #pragma unroll
-        for (int k = 0; k < PREP_TOKENS; ++k) {
-            if (k >= n_here) break;
-            const float x = acc[k];
-            const float log_sig = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
-            decay[(size_t)(t0 + k) * qdim + c] = expf(log_sig * inv_tau);
-            z[(size_t)(t0 + k) * ld + q_col + c] *= q_scale;
-        }
+    for (int k = 0; k < PREP_TOKENS; ++k) {
+        if (k >= n_here) break;
+        const float x = acc[k];
+        const float log_sig = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+        decay[(size_t)(t0 + k) * qdim + c] = expf(log_sig * inv_tau);
+        z[(size_t)(t0 + k) * ld + q_col + c] *= q_scale;
     }
 }
 
@@ -489,8 +504,14 @@ RI_API int ri_gated_linear_attention(float* z, int ld, int q_col, int k_col, int
     if (piece > 0 && (max_pieces <= 0 || scratch == nullptr)) return fail("gated_linear_attention: pieces need scratch");
     const size_t smem = (size_t)PREP_TOKENS * rank * sizeof(float);
     if (smem > 48 * 1024) return fail("gated_linear_attention: a decay of rank %d exceeds the kernel's shared memory", rank);
-    cudaError_t e = launch_dependent(keyed_prepare_kernel, (n_tokens + PREP_TOKENS - 1) / PREP_TOKENS, 256, smem, stream, z, ld,
-                                     q_col, a_col, rank, w2, bias, 1.f / tau, q_scale, decay, n_tokens, qdim);
+    const dim3 prep_grid((n_tokens + PREP_TOKENS - 1) / PREP_TOKENS, (qdim + PREP_CHANNELS - 1) / PREP_CHANNELS);
+    if (prep_grid.y > 65535) return fail("gated_linear_attention: %d key channels exceed the grid limit", qdim);
+    const bool prep_vec = rank % 4 == 0 && (uintptr_t)w2 % 16 == 0;
+    cudaError_t e = prep_vec
+        ? launch_dependent(keyed_prepare_kernel<true>, prep_grid, PREP_CHANNELS, smem, stream, z, ld, q_col, a_col, rank, w2, bias,
+                           1.f / tau, q_scale, decay, n_tokens, qdim)
+        : launch_dependent(keyed_prepare_kernel<false>, prep_grid, PREP_CHANNELS, smem, stream, z, ld, q_col, a_col, rank, w2, bias,
+                           1.f / tau, q_scale, decay, n_tokens, qdim);
     if (check_launch(e, "gated_linear_attention (prepare)")) return 1;
     const ScanCols at{q_col, 0, v_col, k_col, qdim};
     return scan_and_norm<true>(z, ld, decay, at, nullptr, nullptr, norm_w, state, cu_seqlens, seq_slot, o_raw, out, dtype,

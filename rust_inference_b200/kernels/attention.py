@@ -34,7 +34,8 @@ _PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
 # RI_B200_DECODE_ATTENTION=cluster / cp_async / tma forces one of the decode kernels (default: by batch size)
 _DECODE = os.environ.get("RI_B200_DECODE_ATTENTION", "auto")
 # RI_B200_SCORE_FORMS_ATTENTION=generic keeps the generic kernel for scores with a cap, a bias, a sink or a gate;
-# =prefill keeps the prompts' kernel for steps of one token per sequence too
+# =prefill keeps the prompts' kernel for steps of one token per sequence too; =mma_prefill keeps the mma.sync kernel for
+# prompts whose only forms are a cap and kept first positions (which the tcgen05 kernel takes)
 _FORMS = os.environ.get("RI_B200_SCORE_FORMS_ATTENTION", "mma")
 CLUSTER_SPLITS = 8     # a thread-block cluster holds at most 8 CTAs portably
 
@@ -153,7 +154,17 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
                 n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
                 scale=scale, window=window or 0, softcap=softcap, keep_first=keep_first, sink=sink, dist=dist, gate=gate,
                 out_scale=out_scale, n_splits=splits, part_o=part_o, part_ml=part_ml)
-        # prompts and continuations (and single tokens, if asked for)
+        # prompts and continuations (and single tokens, if asked for): a cap and kept first positions alone are forms of
+        # the tcgen05 kernel; a sink, a bias by distance or a gate per head stay with the mma.sync kernel
+        from . import attention_tc
+        if (sink is None and dist is None and gate is None and _FORMS != "mma_prefill" and _PREFILL != "mma"
+                and not (ctx.all_single and _FORMS == "prefill")
+                and attention_tc.supports(head_dim, ctx.page_size, n_heads, n_kv_heads, q_ld, out.shape[1])):
+            return attention_tc.prefill(
+                qkv, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens, out,
+                n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+                page_size=ctx.page_size, scale=scale, window=window or 0, out_scale=out_scale, softcap=softcap,
+                keep_first=keep_first)
         return ops.attention_prefill_forms(
             qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens, out,
             n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,

@@ -35,11 +35,14 @@ def _map(which: int, t: torch.Tensor, rows: int, cols: int, ld: int) -> torch.Te
 
 def prefill(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, page_table, seq_slot, seq_start,
             cu_seqlens, out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int,
-            head_dim: int, page_size: int, scale: float, window: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+            head_dim: int, page_size: int, scale: float, window: int = 0, out_scale: float = 1.0, softcap: float = 0.0,
+            keep_first: int = 0) -> torch.Tensor:
     """bf16 causal attention of every new token over its slot's keys, on tcgen05.  q is the leading
     n_heads * head_dim columns of `qkv`; kcache / vcache are one layer, [pages, kv heads, 64, head_dim].
     `window` is a span: > 0 the last so many keys, < 0 the keys of the query's own block of -window
-    positions.  The result is multiplied by out_scale before it is rounded."""
+    positions.  The result is multiplied by out_scale before it is rounded.  softcap > 0: scores become
+    softcap * tanh(score / softcap) after the scale; keep_first (with a window > 0): the sequence's first so many
+    positions stay visible beyond the window.  Either makes the call take the kernel's form with them."""
     _need_cuda(qkv, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens, out)
     _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
           and qkv.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and out.is_contiguous(),
@@ -49,6 +52,15 @@ def prefill(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, page_
     mk = _map(1, kcache, rows, head_dim, head_dim)
     mv = _map(1, vcache, rows, head_dim, head_dim)
     st = status_word()
+    if softcap or keep_first:
+        _need(softcap >= 0 and keep_first >= 0 and window >= 0 and (window > 0 or not keep_first),
+              "attention_tcgen05: a cap is positive, kept first positions go with a window of the last keys")
+        _call("attention_tcgen05", "ri_attention_tcgen05_prefill_forms", c_void_p(mq.data_ptr()), c_void_p(mk.data_ptr()),
+              c_void_p(mv.data_ptr()), _p(page_table), c_int(page_table.shape[1]), _p(seq_slot), _p(seq_start),
+              _p(cu_seqlens), _p(out), c_int(out.shape[1]), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+              c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_float(out_scale),
+              c_float(softcap), c_int(keep_first), c_void_p(st.data_ptr()), _stream())
+        return out
     _call("attention_tcgen05", "ri_attention_tcgen05_prefill", c_void_p(mq.data_ptr()), c_void_p(mk.data_ptr()),
           c_void_p(mv.data_ptr()), _p(page_table), c_int(page_table.shape[1]), _p(seq_slot), _p(seq_start),
           _p(cu_seqlens), _p(out), c_int(out.shape[1]), c_int(n_seqs), c_int(max_new), c_int(n_heads),
