@@ -15,8 +15,9 @@ from test_redodra_gpu import _drive, d, make_ctx
 # Worst row's max |a - b| / max |b| against the plain model in float64.  float32 runs: a kernel fault shows far above
 # 1e-4.  bfloat16 runs keep bfloat16 activations between the kernels of a sublayer (the stream, the states, the norms,
 # the router and the scores stay float32): rounding alone reaches a few 1e-2 on single rows of a model whose layers
-# run up to ten times; a key too many or too few, a lost state or a wrong expert costs 0.2 and more.
-TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+# run up to ten times (observed: float32 2e-5, bfloat16 1e-2); a key too many or too few, a lost state or a wrong expert
+# costs 0.2 and more.
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 
 pytestmark = pytest.mark.gpu
 

@@ -16,7 +16,7 @@ from conftest import random_tokens, rel_err
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"float32": 1e-4, "bfloat16": 8e-2}
+TOL = {"float32": 1e-4, "bfloat16": 5e-2}        # observed over the fourteen: 2e-5 and 2.4e-2
 
 
 def draw_config(seed: int) -> dict:
