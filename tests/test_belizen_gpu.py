@@ -523,3 +523,83 @@ def test_trace_replay_picks_the_model_by_its_config(models, tmp_path):
     assert not (out / "3.f32").exists()
     assert rel_err(read(4), wa[69:70]) < 1e-4
     assert rel_err(read(5), torch.stack([wc[0], wc[29]])) < 1e-4
+
+
+def test_the_command_line_on_a_belizen_folder(models, tmp_path):
+    """`bin/gguf-infer` as a process: greedy ids from a model folder equal the plain model's, and the random-weights
+    mode runs from a config.json alone (which must then give the decays' rank)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli = os.path.join(root, "bin", "gguf-infer")
+    model = models("B", "float32")
+    prompts = [random_tokens(n, model.cfg["vocab"], 70 + n) for n in (9, 1)]
+    args = [sys.executable, cli, "--model", model.folder, "--temperature", "0", "--repetition-penalty", "1", "--max-tokens", "6",
+            "--dtype", "float32", "--max-seq-len", "256", "--stop-ids", ""]
+    for p in prompts:
+        args += ["--prompt", ",".join(str(t) for t in p)]
+    p = subprocess.run(args, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert [[int(t) for t in l.split()] for l in lines] == [plain_belizen.greedy(model.cfg, model.weights, q, 6) for q in prompts]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(bm.CONFIGS["A"]))
+    p = subprocess.run([sys.executable, cli, "--random-config", str(cfg_file), "--weights-seed", "3", "--random-prompts", "2:4:20",
+                        "-n", "5", "--max-seq-len", "128"], capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len([l for l in p.stdout.splitlines() if l.strip()]) == 2
+
+
+# ---------------------------------------------------------------------------------------------------
+# small kernels alone
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("rows,width,ld,col", [(1, 72, 200, 100), (7, 128, 512, 384), (300, 264, 1000, 8), (5, 33, 90, 41), (2100, 1024, 3080, 2048)])
+def test_sigmoid_gate_in_place(dtype, rows, width, ld, col):
+    """x *= sigmoid(gate columns) * factor: rows that move 16 bytes at a time (widths and offsets that are multiples
+    of 8) and rows that cannot."""
+    from rust_inference_b200.kernels import ops
+    g = torch.Generator().manual_seed(rows + width)
+    x = torch.randn(rows, width, generator=g).to(dtype)
+    wide = (torch.randn(rows, ld, generator=g) * 3.0).to(dtype)
+    want = x.double() * torch.sigmoid(wide.double()[:, col:col + width]) * 0.45
+    got = ops.sigmoid_gate_(d(x), d(wide), col, 0.45)
+    assert rel_err(got, want) < (1e-6 if dtype == F32 else 6e-3)
+
+
+def test_logit_cap_and_stream_add():
+    from rust_inference_b200.kernels import ops
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(37, 301, generator=g) * 40.0
+    got = ops.softcap_(d(x), 17.0)
+    assert torch.allclose(got.cpu().double(), 17.0 * torch.tanh(x.double() / 17.0), atol=2e-5)
+    s, other, row = torch.randn(9, 100, generator=g), torch.randn(9, 100, generator=g), torch.randn(100, generator=g)
+    for o, r in ((other, row), (None, row), (other, None)):
+        want = s.clone() + (o if o is not None else 0) + (r if r is not None else 0)
+        got = ops.stream_add(d(s.clone()), None if o is None else d(o), None if r is None else d(r))
+        assert torch.allclose(got.cpu(), want, atol=1e-6)
+
+
+def test_pass_entry_alone():
+    """What joins the stream at a pass: the pass's vector always, the kept embedding output from the second pass on."""
+    from rust_inference_b200.engine.context import Workspace
+    from rust_inference_b200.parts.registry import lookup
+    width, n = 72, 11
+    part = lookup("stream", "pass_entry")(passes=3, readd_input=True, weight_name="step", hidden_size=width, dtype=BF16, device=DEV)
+    assert {k: tuple(v.shape) for k, v in part.tensor_specs().items()} == {"step": (3, width)}
+    g = torch.Generator().manual_seed(1)
+    step, first = torch.randn(3, width, generator=g), torch.randn(n, width, generator=g)
+    part.set_tensors({"step": d(step)})
+    ctx = _Scratch(Workspace(DEV), BF16)
+    stream = d(first.clone())
+    part.begin(stream, ctx)
+    want = first.clone()
+    for t in range(3):
+        stream += 1.0                                 # a layer's work between the passes
+        want = want + 1.0 + (first if t > 0 else 0) + step[t]
+        part.forward(stream, ctx, t)
+        assert torch.allclose(stream.cpu(), want, atol=1e-5), t
+    with pytest.raises(ValueError):
+        part.forward(stream, ctx, 3)
