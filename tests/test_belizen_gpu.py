@@ -603,3 +603,24 @@ def test_pass_entry_alone():
         assert torch.allclose(stream.cpu(), want, atol=1e-5), t
     with pytest.raises(ValueError):
         part.forward(stream, ctx, 3)
+
+
+@pytest.mark.parametrize("heads,kv,dim,cap,size,keep", [(20, 1, 64, None, 100, 5), (4, 1, 128, None, 64, 64), (8, 2, 64, 9.0, None, None),
+                                                        (40, 2, 64, 9.0, 70, 0), (2, 2, 128, 30.0, 200, 129)])
+def test_tensor_core_sizes_with_each_form_alone(heads, kv, dim, cap, size, keep):
+    """bfloat16 heads of 64 and 128: kept first positions without a cap, a cap without a window, a window and a cap
+    without kept positions, more than 16 query heads to a kv head (whose single tokens take the prompts' kernel), kept
+    positions beyond two pages; a prompt of five pages, then single tokens, then portions."""
+    from rust_inference_b200.cache.sequence_cache import SequenceCache
+    from rust_inference_b200.engine.context import Workspace
+    width, n = 128, 330
+    m = bm.attn(heads=heads, kv=kv, dim=dim, vdim=dim, scale=0.7 / math.sqrt(dim), cap=cap, size=size, keep=keep, base=2000.0, rot=dim // 2,
+                scaling=(3.0, 96, 8.0, 1.0))
+    part, W, p = _part("mixer", bm.layer("attention", m), BF16, width, seed=heads + dim)
+    cache = SequenceCache([part.cache_request()], max_tokens=1024, max_seq_len=512, dtype=BF16, device=DEV, n_slots=2)
+    ws = Workspace(DEV)
+    g = torch.Generator().manual_seed(dim)
+    x = (torch.randn(n, width, generator=g) * 0.5).to(BF16)
+    want = plain_belizen.attention_mixer(x.double(), W, p, m, 1e-5)
+    for portions in ([n], [300, 1], [1, 2, 60, 1, 64, 5, 130, 67]):
+        assert rel_err(_drive(part, cache, x, portions, BF16, ws), want) < 3e-2, portions
