@@ -89,13 +89,19 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // offset), the gates f in the rows of fz (which may be z itself) at f_col.
 struct ScanCols { int q_col, f_col, v_col, k_col, f_ld; };
 
+// The keyed form's decays and query scale for the one-pass scan, which forms them in its tile (no kernel of their own
+// for a step's few tokens): decay = sigmoid(bias + w2 a)^(1/tau) with a = the `rank` values at a_col of a token's row
+// of z, and q times q_scale.  w2 == nullptr: the gates come from memory as they are.
+struct KeyedPrep { const float* w2; const float* bias; int rank, a_col; float inv_tau, q_scale; };
+
 template <int ROWS, bool VEC, int mode, bool KEYED>
 __global__ void __launch_bounds__(SCAN_THREADS)
 recurrence_scan_kernel(const float* z, int ld, const float* fz, ScanCols at, float* __restrict__ o_raw, float* state,
                        float* piece_state, float* piece_gates, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, int heads, int dim, int vdim, int piece, int max_pieces,
-                       int tile_t, const float* __restrict__ prep_bias, const float* __restrict__ prep_low) {
+                       int tile_t, const float* __restrict__ prep_bias, const float* __restrict__ prep_low, KeyedPrep keyed) {
     using Tile = ScanTile<ROWS, KEYED>;
+    const bool forms_decays = KEYED && mode == WHOLE && keyed.w2 != nullptr;
     extern __shared__ __align__(16) float tile[];
     const int b = blockIdx.x / max_pieces, c = blockIdx.x % max_pieces, h = blockIdx.y;
     const int r = threadIdx.x % R, jj = threadIdx.x / R;
@@ -146,7 +152,8 @@ recurrence_scan_kernel(const float* z, int ld, const float* fz, ScanCols at, flo
                 float* base = tile + tok * Tile::TOKEN;
                 if (it < dq) {
                     const int ch = 4 * it;
-                    cp_async16(base + (ch / ROWS) * Tile::SLICE + ch % ROWS, fz + (size_t)(tb + tok) * f_ld + f_off + ch);
+                    if (!forms_decays)
+                        cp_async16(base + (ch / ROWS) * Tile::SLICE + ch % ROWS, fz + (size_t)(tb + tok) * f_ld + f_off + ch);
                 } else if (it < 2 * dq) {
                     const int ch = 4 * (it - dq);
                     if (mode != LOCAL)                            // a piece's end state needs no q
@@ -167,14 +174,30 @@ recurrence_scan_kernel(const float* z, int ld, const float* fz, ScanCols at, flo
                 const int tok = idx / per, it = idx % per;
                 const float* row = z + (size_t)(tb + tok) * ld;
                 float* base = tile + tok * Tile::TOKEN;
-                if (it < dim) base[(it / ROWS) * Tile::SLICE + it % ROWS] = fz[(size_t)(tb + tok) * f_ld + f_off + it];
-                else if (it < 2 * dim) base[R * Tile::SLICE + ((it - dim) / ROWS) * Tile::SLICE + (it - dim) % ROWS] = row[q_off + it - dim];
+                if (it < dim) {
+                    if (!forms_decays) base[(it / ROWS) * Tile::SLICE + it % ROWS] = fz[(size_t)(tb + tok) * f_ld + f_off + it];
+                } else if (it < 2 * dim) base[R * Tile::SLICE + ((it - dim) / ROWS) * Tile::SLICE + (it - dim) % ROWS] = row[q_off + it - dim];
                 else if (KEYED && it < 3 * dim)
                     base[2 * R * Tile::SLICE + ((it - 2 * dim) / ROWS) * Tile::SLICE + (it - 2 * dim) % ROWS] = row[k_off + it - 2 * dim];
                 else base[Tile::V_AT + it - parts * dim] = row[v_off + it - parts * dim];
             }
         }
         __syncthreads();
+        if (forms_decays) {
+            // the keyed form's decays of this head's channels and the queries' scale, in the tile
+            for (int idx = threadIdx.x; idx < n_tok * dim; idx += SCAN_THREADS) {
+                const int tok = idx / dim, ch = idx % dim;
+                const float* a = z + (size_t)(tb + tok) * ld + keyed.a_col;
+                const float* w = keyed.w2 + (size_t)(h * dim + ch) * keyed.rank;
+                float acc = keyed.bias[h * dim + ch];
+                for (int rr = 0; rr < keyed.rank; ++rr) acc = fmaf(w[rr], a[rr], acc);
+                const float log_sig = fminf(acc, 0.f) - log1pf(expf(-fabsf(acc)));
+                float* base = tile + tok * Tile::TOKEN + (ch / ROWS) * Tile::SLICE + ch % ROWS;
+                base[0] = expf(log_sig * keyed.inv_tau);
+                base[R * Tile::SLICE] *= keyed.q_scale;
+            }
+            __syncthreads();
+        }
         if (!KEYED && mode == WHOLE && prep_bias != nullptr) {
             // the one-pass form applies the activations itself (no kernel of its own for a step's few tokens):
             // f <- low + (1 - low) sigmoid(f + bias), q <- silu(q), in the tile
@@ -364,7 +387,7 @@ template <int ROWS, bool KEYED>
 int launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld, const float* fz, ScanCols at, float* o_raw,
                 float* state, float* piece_state, float* piece_gates, const int* cu_seqlens, const int* seq_slot, int heads,
                 int dim, int vdim, int mode, int piece, int max_pieces, int longest, const float* prep_bias,
-                const float* prep_low) {
+                const float* prep_low, KeyedPrep keyed) {
     const int token_bytes = ScanTile<ROWS, KEYED>::TOKEN * (int)sizeof(float);
     int tile_t = SCAN_SMEM_LIMIT / token_bytes;
     if (tile_t > 64) tile_t = 64;
@@ -379,7 +402,7 @@ int launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld
         if (int rc = raise_dynamic_smem(kernel, SCAN_SMEM_LIMIT, once, "gated_recurrence")) return rc;                    \
         e = launch_dependent(kernel, grid, SCAN_THREADS, smem, stream, z, ld, fz, at, o_raw, state, piece_state,          \
                              piece_gates, cu_seqlens, seq_slot, heads, dim, vdim, piece, max_pieces, tile_t, prep_bias,   \
-                             prep_low);                                                                                   \
+                             prep_low, keyed);                                                                            \
     }
     if (vec) {
         if (mode == WHOLE) RI_LAUNCH(true, WHOLE) else if (mode == LOCAL) RI_LAUNCH(true, LOCAL) else RI_LAUNCH(true, FINAL)
@@ -397,7 +420,7 @@ int scan_and_norm(const float* z, int ld, const float* fz, ScanCols at, const fl
                   const float* norm_w, float* state, const int* cu_seqlens, const int* seq_slot, float* o_raw, void* out,
                   int dtype, int n_tokens, int n_seqs, int heads, int dim, int vdim, float eps, float out_scale, int piece,
                   int max_pieces, float* scratch, int longest_run, const float* gate, int gate_ld, int gate_col,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, KeyedPrep keyed = KeyedPrep{nullptr, nullptr, 0, 0, 0.f, 1.f}) {
     int rows = (dim + R - 1) / R;
     rows = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : rows <= 32 ? 32 : 64;
     const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && at.f_ld % 4 == 0 && (uintptr_t)z % 16 == 0 &&
@@ -412,7 +435,7 @@ int scan_and_norm(const float* z, int ld, const float* fz, ScanCols at, const fl
         const int longest = mode == WHOLE ? (longest_run > 0 ? longest_run : n_tokens) : piece;
 #define RI_SCAN(ROWS) launch_scan<ROWS, KEYED>(vec, grid, stream, z, ld, fz, at, o_raw, state, piece_state, piece_gates,        \
                                                cu_seqlens, seq_slot, heads, dim, vdim, mode, piece > 0 ? piece : 1, mp, longest, \
-                                               mode == WHOLE ? prep_bias : nullptr, mode == WHOLE ? prep_low : nullptr)
+                                               mode == WHOLE ? prep_bias : nullptr, mode == WHOLE ? prep_low : nullptr, keyed)
         if (rows == 4) return RI_SCAN(4);
         if (rows == 8) return RI_SCAN(8);
         if (rows == 16) return RI_SCAN(16);
@@ -485,7 +508,8 @@ RI_API int ri_gated_recurrence(float* z, int ld, const float* bias, const float*
 // touched them: queries at q_col, keys at k_col (heads*dim each), values at v_col and the result's gates at g_col
 // (heads*vdim each), the decay's low-rank input at a_col (rank values).  w2: float32 [heads*dim, rank], bias: float32
 // [heads*dim]: decay = sigmoid(w2 a + bias)^(1/tau) into `decay` (float32 [n_tokens, heads*dim], scratch); the queries
-// are scaled by q_scale in place.  Then S <- diag(decay) S + k v^T, o = S^T q per head from the slot's state, and
+// are scaled by q_scale in place.  Without pieces (a step's few tokens) the one-pass scan forms decays and scaled
+// queries in its tile instead, and neither `decay` nor z is written.  Then S <- diag(decay) S + k v^T, o = S^T q per head from the slot's state, and
 // out = o / rms(o) * norm_w * silu(gate) * out_scale per head.  Pieces, scratch, o_raw, longest_run: as above.
 RI_API int ri_gated_linear_attention(float* z, int ld, int q_col, int k_col, int v_col, int g_col, int a_col, int rank,
                                      const float* w2, const float* bias, float tau, float q_scale, float* decay,
@@ -506,6 +530,11 @@ RI_API int ri_gated_linear_attention(float* z, int ld, int q_col, int k_col, int
     if (smem > 48 * 1024) return fail("gated_linear_attention: a decay of rank %d exceeds the kernel's shared memory", rank);
     const dim3 prep_grid((n_tokens + PREP_TOKENS - 1) / PREP_TOKENS, (qdim + PREP_CHANNELS - 1) / PREP_CHANNELS);
     if (prep_grid.y > 65535) return fail("gated_linear_attention: %d key channels exceed the grid limit", qdim);
+    const ScanCols at{q_col, 0, v_col, k_col, qdim};
+    if (piece <= 0)           // a step's few tokens: the one-pass scan forms the decays in its tile
+        return scan_and_norm<true>(z, ld, decay, at, nullptr, nullptr, norm_w, state, cu_seqlens, seq_slot, o_raw, out, dtype,
+                                   n_tokens, n_seqs, heads, dim, vdim, eps, out_scale, piece, max_pieces, scratch, longest_run, z,
+                                   ld, g_col, stream, KeyedPrep{w2, bias, rank, a_col, 1.f / tau, q_scale});
     const bool prep_vec = rank % 4 == 0 && (uintptr_t)w2 % 16 == 0;
     cudaError_t e = prep_vec
         ? launch_dependent(keyed_prepare_kernel<true>, prep_grid, PREP_CHANNELS, smem, stream, z, ld, q_col, a_col, rank, w2, bias,
@@ -513,7 +542,6 @@ RI_API int ri_gated_linear_attention(float* z, int ld, int q_col, int k_col, int
         : launch_dependent(keyed_prepare_kernel<false>, prep_grid, PREP_CHANNELS, smem, stream, z, ld, q_col, a_col, rank, w2, bias,
                            1.f / tau, q_scale, decay, n_tokens, qdim);
     if (check_launch(e, "gated_linear_attention (prepare)")) return 1;
-    const ScanCols at{q_col, 0, v_col, k_col, qdim};
     return scan_and_norm<true>(z, ld, decay, at, nullptr, nullptr, norm_w, state, cu_seqlens, seq_slot, o_raw, out, dtype,
                                n_tokens, n_seqs, heads, dim, vdim, eps, out_scale, piece, max_pieces, scratch, longest_run, z, ld,
                                g_col, stream);

@@ -755,7 +755,7 @@ def gated_linear_attention(z: torch.Tensor, *, q_col: int, k_col: int, v_col: in
           c_int(n), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), c_int(piece),
           c_int(max_pieces), _p(scratch if piece > 0 else None), c_int(max(0, min(int(longest_run), n))), _stream())
     global _launches
-    _launches += 5 if piece > 0 else 3
+    _launches += 5 if piece > 0 else 2
     return out
 
 
