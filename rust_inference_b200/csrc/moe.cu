@@ -68,13 +68,18 @@ template <> __device__ __forceinline__ void load4_f32<__nv_bfloat16>(const __nv_
 // the shared expert's gate row): a row is read once and multiplied with every token of the block, four
 // values at a time with as many independent sums as tokens.  Then warp k makes token k's choice.
 // Shared memory per token: score[E], choice[E], group score[G].
+// A step of few tokens (one per block) may cut the router's rows over gridDim.y blocks per token, so that more SMs than
+// tokens read them: every block leaves its rows' sums in `split_sums` ([tokens, experts + 1], float32) and takes a ticket
+// from the token's counter in `split_count` (int32, zero before and after the kernel); the block that draws the last
+// ticket reads all sums back and makes the token's choice.
 template <typename T, bool VEC, int TOK>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* x, const float* __restrict__ router, const float* __restrict__ correction,
                  const float* __restrict__ gate_w, int* __restrict__ ids, float* __restrict__ weights,
                  float* __restrict__ gate_out, int n_tokens, int width, int experts, int top, int groups, int keep,
-                 int per_block, int form) {
+                 int per_block, int form, float* split_sums, int* split_count) {
     extern __shared__ float smem[];
+    __shared__ int last_ticket;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stride = 2 * experts + groups;
     let_next_kernel_start();
@@ -82,7 +87,21 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
     const int tok0 = blockIdx.x * per_block;
     const int n_here = min(per_block, n_tokens - tok0);
 
-    for (int e = warp; e < experts + (gate_w != nullptr ? 1 : 0); e += ROUTE_WARPS) {
+    const int n_rows = experts + (gate_w != nullptr ? 1 : 0);
+    const bool split = gridDim.y > 1;                 // only with one token per block
+    const int rows_each = (n_rows + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int row_lo = split ? (int)blockIdx.y * rows_each : 0, row_hi = split ? min(n_rows, row_lo + rows_each) : n_rows;
+    // what a row's sum becomes: the score (or, for the softmax, the logit) and the choice score; the gate's sigmoid
+    auto place = [&](int k, int e, float a) {
+        const float s = sigmoid_f32(a);
+        if (e < experts) {
+            smem[k * stride + e] = (form & 1) ? a : s;           // softmax: the logit, turned into a score below
+            smem[k * stride + experts + e] = s + correction[e];
+        } else {
+            gate_out[tok0 + k] = s;
+        }
+    };
+    for (int e = row_lo + warp; e < row_hi; e += ROUTE_WARPS) {
         const float* w = e < experts ? router + (size_t)e * width : gate_w;
         float acc[TOK];
 #pragma unroll
@@ -112,15 +131,20 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
             if (k >= n_here) break;
             const float a = warp_sum(acc[k]);
             if (lane == 0) {
-                const float s = sigmoid_f32(a);
-                if (e < experts) {
-                    smem[k * stride + e] = (form & 1) ? a : s;           // softmax: the logit, turned into a score below
-                    smem[k * stride + experts + e] = s + correction[e];
-                } else {
-                    gate_out[tok0 + k] = s;
-                }
+                if (split) split_sums[(size_t)(tok0 + k) * (experts + 1) + e] = a;
+                else place(k, e, a);
             }
         }
+    }
+    if (split) {
+        __threadfence();                               // this block's sums are visible before its ticket is
+        __syncthreads();
+        if (threadIdx.x == 0) last_ticket = atomicAdd(&split_count[tok0], 1);
+        __syncthreads();
+        if (last_ticket != (int)gridDim.y - 1) return;
+        __threadfence();
+        for (int e = threadIdx.x; e < n_rows; e += blockDim.x) place(0, e, __ldcg(split_sums + (size_t)tok0 * (experts + 1) + e));
+        if (threadIdx.x == 0) split_count[tok0] = 0;   // zero again for the next launch
     }
     __syncthreads();
     if (warp >= n_here) return;
@@ -378,9 +402,12 @@ __global__ void moe_combine_kernel(float* residual, const float* y, const float*
 }  // namespace
 
 // form: bit 0 softmax scores instead of sigmoid ones, bit 1 weights not divided by their sum.
+// split > 1 (steps of up to ROUTE_SPLIT_TOKENS tokens): the router's rows are cut over that many blocks per token;
+// split_sums: float32 [n_tokens, experts + 1] scratch, split_count: int32 [n_tokens], zero before the call and after it.
 RI_API int ri_moe_route(const void* x, int dtype, const float* router, const float* correction, const float* gate_w,
                         int* ids, float* weights, float* gate_out, int n_tokens, int width, int experts, int top,
-                        int groups, int keep, int form, cudaStream_t stream) {
+                        int groups, int keep, int form, int split, float* split_sums, int* split_count,
+                        cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (experts <= 0 || top <= 0 || top > experts) return fail("moe_route: top %d of %d experts", top, experts);
     if (groups <= 0 || experts % groups || keep <= 0 || keep > groups)
@@ -389,15 +416,17 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
         return fail("moe_route: %d groups of %d experts cannot give %d choices", keep, experts / groups, top);
     // few tokens: one per block, so that the router's rows are shared out over more SMs
     const int per_block = n_tokens >= 148 * ROUTE_TOKENS ? ROUTE_TOKENS : (n_tokens >= 2 * 148 ? 2 : 1);
+    if (split > 1 && (per_block != 1 || split_sums == nullptr || split_count == nullptr || split > 65535))
+        return fail("moe_route: rows cut over %d blocks need one token per block and their scratch", split);
     const size_t smem = (size_t)per_block * (2 * experts + groups) * sizeof(float);
     if (smem > 48 * 1024) return fail("moe_route: %d experts exceed the router kernel's shared memory", experts);
-    const int blocks = (n_tokens + per_block - 1) / per_block;
+    const dim3 blocks((n_tokens + per_block - 1) / per_block, split > 1 ? split : 1);
     const bool vec = width % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)router % 16 == 0 &&
                      (gate_w == nullptr || (uintptr_t)gate_w % 16 == 0);
     cudaError_t e;
 #define RI_ROUTE_N(T, V, N) launch_dependent(moe_route_kernel<T, V, N>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)x, \
                                              router, correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top,   \
-                                             groups, keep, per_block, form)
+                                             groups, keep, per_block, form, split_sums, split_count)
 #define RI_ROUTE(T, V) (per_block == 1 ? RI_ROUTE_N(T, V, 1) : per_block == 2 ? RI_ROUTE_N(T, V, 2) : RI_ROUTE_N(T, V, ROUTE_TOKENS))
     if (dtype == RI_F32) e = vec ? RI_ROUTE(float, true) : RI_ROUTE(float, false);
     else if (dtype == RI_BF16) e = vec ? RI_ROUTE(__nv_bfloat16, true) : RI_ROUTE(__nv_bfloat16, false);

@@ -188,7 +188,8 @@ def time_parts(engine, kind: str, s: dict, lens_before: list, new_tokens: int, p
             ms_down = timer(lambda: ops.moe_grouped_simt(act, ff.w_down, None, y, offsets, order, tiles, n_tiles,
                                                          n_pairs=pairs, top=top))
         out["route_ms"] = round(timer(lambda: ops.moe_route(x, ff.router, ff.correction, ids, wts, top=top, groups=s["groups"],
-                                                            keep=s["keep"], gate_weight=ff.shared_mix, gate_out=gate)), 4)
+                                                            keep=s["keep"], gate_weight=ff.shared_mix, gate_out=gate,
+                                                            **ff.route_cut(n, ctx))), 4)
         out["arrange_ms"] = round(timer(lambda: ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles, place)), 4)
         if fast:
             out["gather_ms"] = round(timer(lambda: ops.moe_gather(x, xs, order, n_pairs=pairs, top=top)), 4)

@@ -139,7 +139,7 @@ def time_parts(engine, s: dict, lens_before: list, new_tokens: int, peaks: dict,
     pairs = n * top
     ids = torch.empty(n, top, dtype=torch.int32, device=dev)
     wts = torch.empty(n, top, dtype=f32, device=dev)
-    route = lambda: ops.moe_route(x, mx.router, mx.correction, ids, wts, top=top, softmax=True, normalise=False)
+    route = lambda: ops.moe_route(x, mx.router, mx.correction, ids, wts, top=top, softmax=True, normalise=False, **mx.route_cut(n, ctx))
     row("router", timer(route), 0.0, outputs * width * 4 + n * width * 2, fp32_flops=2.0 * n * outputs * width)
     real = int((ids < experts).sum())
     used = int(torch.unique(ids[ids < experts]).numel())

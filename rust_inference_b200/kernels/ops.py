@@ -765,12 +765,15 @@ def gated_linear_attention(z: torch.Tensor, *, q_col: int, k_col: int, v_col: in
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, ids: torch.Tensor,
               weights: torch.Tensor, *, top: int, groups: int = 1, keep: int = 1,
               gate_weight: torch.Tensor | None = None, gate_out: torch.Tensor | None = None,
-              softmax: bool = False, normalise: bool = True) -> None:
+              softmax: bool = False, normalise: bool = True, split: int = 1, split_sums: torch.Tensor | None = None,
+              split_count: torch.Tensor | None = None) -> None:
     """Per token the `top` experts with the largest sigmoid(router x) + correction among the `keep` best of
     `groups` groups (a group's score: the sum of its two largest), ids int32 [T, top], and their weights
     float32 [T, top] (the plain sigmoid scores, normalised).  gate_weight float32 [width]: gate_out[t] =
     sigmoid(gate_weight . x_t) as well.  softmax: the scores are softmax(router x) over all experts instead of
-    sigmoids; normalise False: the weights are the chosen scores as they are."""
+    sigmoids; normalise False: the weights are the chosen scores as they are.  split > 1 (steps of fewer than 296
+    tokens): the router's rows are cut over that many blocks per token, which leave their sums in split_sums (float32
+    [T, experts + 1]) and count themselves in split_count (int32 [T], zero before the call and after it)."""
     _need_cuda(x, router, correction, ids, weights, gate_weight, gate_out)
     n, width = x.shape
     experts = router.shape[0]
@@ -782,9 +785,15 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, i
     if gate_weight is not None:
         _need(gate_weight.dtype == torch.float32 and gate_weight.is_contiguous() and gate_weight.numel() == width
               and gate_out.dtype == torch.float32 and gate_out.numel() >= n, "moe_route: gate")
+    if split > 1:
+        _need_cuda(split_sums, split_count)
+        _need(n < 296 and split_sums is not None and split_sums.dtype == torch.float32 and split_sums.is_contiguous()
+              and split_sums.numel() >= n * (experts + 1) and split_count is not None and split_count.dtype == torch.int32
+              and split_count.numel() >= n, "moe_route: rows cut over blocks need few tokens, float32 sums and int32 counters")
     _call("moe", "ri_moe_route", _p(x), c_int(dtype_code(x.dtype)), _p(router), _p(correction), _p(gate_weight), _p(ids),
           _p(weights), _p(gate_out), c_int(n), c_int(width), c_int(experts), c_int(top), c_int(groups), c_int(keep),
-          c_int((1 if softmax else 0) | (0 if normalise else 2)), _stream())
+          c_int((1 if softmax else 0) | (0 if normalise else 2)), c_int(max(1, split)), _p(split_sums if split > 1 else None),
+          _p(split_count if split > 1 else None), _stream())
 
 
 def moe_tile_rows() -> int:

@@ -124,6 +124,8 @@ class RoutedExperts(FeedForward):
     # the fallback for other sizes
     TENSOR_CORE_MIN_TOKENS = 0
     GATHER_IN_ARRANGE_PAIRS = 256       # up to so many (token, choice) pairs the arranging block also gathers their rows
+    ROUTE_SPLIT_TOKENS, ROUTE_SPLIT_BLOCKS, ROUTE_SPLIT_MOST = 64, 148, 16     # steps of up to 64 tokens: the router's rows
+    #                                     over up to 16 blocks per token, about one block per SM in all
 
     def _on_tensor_cores(self, x) -> bool:
         if x.dtype != torch.bfloat16 or x.shape[0] <= self.TENSOR_CORE_MIN_TOKENS:
@@ -132,15 +134,28 @@ class RoutedExperts(FeedForward):
         return (tcgen05.grouped_supports(x.dtype, self.w_gate) and tcgen05.grouped_supports(x.dtype, self.w_down)
                 and self.hidden_size % 8 == 0)
 
+    def route_cut(self, n: int, ctx) -> dict:
+        """Keyword arguments of `ops.moe_route` for a step of n tokens: a step of few tokens cuts the router's rows over
+        several blocks per token, so that more SMs than tokens read them (scratch from the step's workspace)."""
+        outputs = self.router.shape[0] + (1 if self.shared_mix is not None else 0)
+        if n > self.ROUTE_SPLIT_TOKENS:
+            return {}
+        split = min(self.ROUTE_SPLIT_MOST, self.ROUTE_SPLIT_BLOCKS // n, outputs // 4)
+        if split <= 1:
+            return {}
+        return dict(split=split, split_sums=ctx.buffer("moe_route_sums", (n, self.router.shape[0] + 1), torch.float32),
+                    split_count=ctx.zeroed_buffer("moe_route_count", (n,), torch.int32))
+
     def forward(self, x, residual, ctx):
         n, h, top, experts = x.shape[0], self.hidden_size, self.top, self.n_experts
         pairs = n * top
         ids = ctx.buffer("moe_ids", (n, top), torch.int32)
         weights = ctx.buffer("moe_weights", (n, top), torch.float32)
         gate = ctx.buffer("moe_shared_gate", (n,), torch.float32) if self.shared_mix is not None else None
+        cut = self.route_cut(n, ctx)
         ops.moe_route(x, self.router, self.correction, ids, weights, top=top, groups=self.n_groups,
                       keep=self.group_keep, gate_weight=self.shared_mix, gate_out=gate,
-                      softmax=self.router_kind == "softmax", normalise=self.normalise)
+                      softmax=self.router_kind == "softmax", normalise=self.normalise, **cut)
         fast = self._on_tensor_cores(x)
         if fast:
             from ..kernels import tcgen05

@@ -124,17 +124,22 @@ def test_softmax_router_with_pass_through_experts(dtype, experts, identity, top,
 def test_router_choice_and_weights():
     """The routing kernel against the plain router: ids in the order of the choice, weights the plain scores."""
     from rust_inference_b200.kernels import ops
-    for n, width, outputs, top in ((1, 72, 5, 1), (9, 128, 12, 4), (700, 100, 33, 6), (3000, 64, 3, 3)):
+    for n, width, outputs, top in ((1, 72, 5, 1), (9, 128, 12, 4), (40, 256, 70, 8), (700, 100, 33, 6), (3000, 64, 3, 3)):
         g = torch.Generator().manual_seed(n)
         x = torch.randn(n, width, generator=g)
         router = torch.randn(outputs, width, generator=g) / math.sqrt(width) * 2
         corr = 0.1 * torch.randn(outputs, generator=g)
         ids, weights = plain_belizen.route(x.double(), router.double(), corr.double(), top)
-        got_ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
-        got_w = torch.empty(n, top, dtype=torch.float32, device=DEV)
-        ops.moe_route(d(x), d(router), d(corr), got_ids, got_w, top=top, softmax=True, normalise=False)
-        assert torch.equal(got_ids.cpu().long(), ids)
-        assert torch.allclose(got_w.cpu().double(), weights, rtol=2e-5, atol=1e-7)
+        sums = torch.empty(n, outputs + 1, dtype=torch.float32, device=DEV)
+        count = torch.zeros(n, dtype=torch.int32, device=DEV)
+        for split in ((1, 2, 5, 16) if n < 296 else (1,)):          # the router's rows over so many blocks per token
+            got_ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
+            got_w = torch.empty(n, top, dtype=torch.float32, device=DEV)
+            ops.moe_route(d(x), d(router), d(corr), got_ids, got_w, top=top, softmax=True, normalise=False, split=split,
+                          split_sums=sums, split_count=count)
+            assert torch.equal(got_ids.cpu().long(), ids), split
+            assert torch.allclose(got_w.cpu().double(), weights, rtol=2e-5, atol=1e-7), split
+            assert int(count.abs().sum()) == 0                       # the counters are zero again
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
